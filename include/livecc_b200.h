@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define LCC_ABI_VERSION 8
+#define LCC_ABI_VERSION 9
 #define LCC_PAGE_SIZE 64
 
 typedef struct lcc_ctx lcc_ctx;
@@ -290,6 +290,90 @@ int lcc_resize_plan_info(const lcc_resize_plan* plan, int* rows_per_cta, int* ma
 /* src: device uint8 [planes, h, w] (planes = T*C), dst: device uint8 [planes, H, W]. One kernel. */
 int lcc_resize_bicubic_aa_u8(lcc_ctx* ctx, const lcc_resize_plan* plan, const uint8_t* src, int planes, uint8_t* dst,
                              lcc_stream_t stream);
+
+/* ---- hybrid sequence models: decoder-only language models whose layers mix tokens with a state-space recurrence, gated
+ * linear attention or chunk-local attention instead of (or beside) full attention. A layer is
+ *     x <- norm1(alpha * x + mixer(x)),  then (if it has a feed-forward)  x <- norm2(alpha * x + ff(x))       (post-norm)
+ * with the residual stream, every norm, every score and every recurrent state in fp32. One library serves two storage
+ * types: LCC_DT_BF16 (bf16 weights, activations and K/V pages; fp32 accumulation) and LCC_DT_F32 (everything fp32, plain
+ * FMAs). The caller owns all memory: weights, workspace, K/V pages and the fp32 recurrent-state slots of every sequence. */
+#define LCC_DT_BF16 0
+#define LCC_DT_F32 1
+#define LCC_MIX_SSD 1      /* scalar-decay state-space layer: in-proj -> causal conv + silu -> recurrence -> gated grouped norm -> out-proj */
+#define LCC_MIX_PARALLEL 2 /* chunk-local sink attention (left) beside gated linear attention (right), averaged after a norm each */
+
+typedef struct {
+    int32_t type; /* LCC_MIX_* */
+    int32_t ff;   /* feed-forward width, 0 = the layer has none */
+    /* LCC_MIX_SSD: heads x vdim value channels, `state` key channels shared by heads / groups heads, `conv` taps */
+    int32_t s_heads, s_vdim, s_state, s_groups, s_conv, s_norm_groups;
+    /* LCC_MIX_PARALLEL, left: Hq query heads over G key/value heads, key size dim, value size vdim, chunk (<= 0: none) */
+    int32_t l_heads, l_kv_heads, l_dim, l_vdim, l_chunk;
+    float l_scale;
+    /* LCC_MIX_PARALLEL, right: heads x dim key channels, heads x vdim value channels, decay bottleneck rank, temperature tau */
+    int32_t r_heads, r_dim, r_vdim, r_rank;
+    float r_tau;
+    /* weights: matrices [out, in] in the model's storage type; everything named *_f32 is fp32 */
+    const float *norm1_f32, *norm2_f32;
+    const void* s_in;          /* [2*inner + 2*groups*state + heads, width], rows [z | x | B | C | dt] */
+    const float *s_conv_w_f32, *s_conv_b_f32; /* [inner + 2*groups*state, conv], [..] */
+    const float *s_dt_bias_f32, *s_a_log_f32, *s_skip_f32, *s_norm_f32; /* [heads] x3, [inner] */
+    const void* s_out;         /* [width, inner] */
+    const void* l_in;          /* [Hq*dim + G*dim + G*vdim + Hq, width], rows [q | k | v | gate] */
+    const float* l_in_bias_f32; /* same length, zeros for the gate rows */
+    const float *l_qnorm_f32, *l_knorm_f32; /* [Hq*dim], [G*dim] */
+    const void* l_out;         /* [width, Hq*vdim] */
+    const float* l_branch_norm_f32; /* [width] */
+    const void* r_in;          /* [2*heads*dim + 2*heads*vdim + rank, width], rows [q | k | v | gate | decay-down] */
+    const void* r_decay_up;    /* [heads*dim, rank] */
+    const float* r_decay_bias_f32; /* [heads*dim] */
+    const float* r_norm_f32;   /* [vdim], shared by the heads */
+    const void* r_out;         /* [width, heads*vdim] */
+    const float* r_branch_norm_f32; /* [width] */
+    const void* ff_in;         /* [2*ff, width], rows [gate | up]; act = gelu_tanh(gate) * up */
+    const void* ff_out;        /* [width, ff] */
+} lcc_seq_layer;
+
+typedef struct {
+    int32_t width, vocab, n_layers, dtype;
+    float eps, alpha, embed_scale, logit_softcap; /* logit_softcap <= 0: none */
+    const void* embed;          /* [vocab, width] */
+    const float* inv_freq_f32;  /* [width/2]: sinusoidal position frequencies, computed by the host */
+    const float* final_norm_f32;
+    const void* head;           /* [vocab, width] */
+    const lcc_seq_layer* layers;
+} lcc_seq_model_desc;
+
+/* One sequence's part of a step: n_new tokens that follow `past` cached ones. layer_state[i]: this sequence's fp32 state
+ * slot of layer i (SSD: [conv carry: channels x (conv-1)] then [heads x vdim x state]; PARALLEL: [heads x vdim x dim] of
+ * the right mixer), zero at the start of a sequence. k_pages[i] / v_pages[i]: the layer's page pools
+ * [page][kv_heads][page_size][dim|vdim] (NULL for layers without attention); page_table: logical -> physical page.
+ * scalars (optional, device int32[LCC_SC_COUNT]): when given, kernels read the number of cached tokens from scalars[LCC_SC_KV_LEN]
+ * and the ids from ids[scalars[LCC_SC_SEQ_LEN] - n_new ...], and do nothing once scalars[LCC_SC_FINISHED] is set, so that a
+ * decode step can be replayed from a CUDA graph; otherwise `past` and ids[0..n_new) are used. */
+typedef struct {
+    int32_t n_new, past;
+    const int64_t* ids;
+    const int32_t* page_table;
+    int32_t* scalars;
+    float* const* layer_state;
+    void* const* k_pages;
+    void* const* v_pages;
+} lcc_seq_entry;
+
+typedef struct lcc_seq_model lcc_seq_model;
+lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc);
+void lcc_seq_model_destroy(lcc_seq_model* m);
+size_t lcc_seq_workspace_bytes(const lcc_seq_model* m, int max_tokens, int max_want);
+int lcc_seq_bind_workspace(lcc_seq_model* m, void* ws, size_t ws_bytes, int max_tokens, int max_want);
+/* fp32 elements of one sequence's state slot of layer i (0 for none). */
+int64_t lcc_seq_layer_state_floats(const lcc_seq_model* m, int layer);
+/* One step over the concatenated new tokens of all entries (linear layers and row ops run over all rows at once, the
+ * sequence mixers per entry). want_rows: device int32[n_want] row indices into the concatenation whose logits are
+ * wanted; logits: device fp32 [n_want, vocab] (soft cap applied); logits_copy: optional second copy. layer_dump: optional
+ * device fp32 [n_layers, rows, width], the residual stream after every layer. */
+int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entries, int page_size, const int32_t* want_rows,
+                    int n_want, float* logits, float* logits_copy, float* layer_dump, lcc_stream_t stream);
 
 /* Debug/parity hooks: byte offsets of buffers inside the bound workspace. */
 #define LCC_WS_PREFILL_HIDDEN 0 /* bf16 [S, hidden] residual stream of the last prefill */

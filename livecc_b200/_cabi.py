@@ -13,7 +13,7 @@ PKG_DIR = Path(__file__).resolve().parent
 LIB_PATH = PKG_DIR / "liblivecc_sm100a.so"
 HEADER_PATH = PKG_DIR.parent / "include" / "livecc_b200.h"
 
-ABI_VERSION = 8
+ABI_VERSION = 9
 PAGE_SIZE = 64
 
 # epilogue codes (LCC_EPI_*)
@@ -63,7 +63,38 @@ class StreamState(C.Structure):
                 ("page_table", C.c_void_p), ("scalars", C.c_void_p), ("seq", C.c_void_p)]
 
 
-_lib = None
+class SeqLayer(C.Structure):
+    """lcc_seq_layer"""
+    _fields_ = [("type", C.c_int32), ("ff", C.c_int32)] + \
+               [(n, C.c_int32) for n in ("s_heads", "s_vdim", "s_state", "s_groups", "s_conv", "s_norm_groups",
+                                         "l_heads", "l_kv_heads", "l_dim", "l_vdim", "l_chunk")] + \
+               [("l_scale", C.c_float)] + [(n, C.c_int32) for n in ("r_heads", "r_dim", "r_vdim", "r_rank")] + \
+               [("r_tau", C.c_float)] + \
+               [(n, C.c_void_p) for n in ("norm1_f32", "norm2_f32", "s_in", "s_conv_w_f32", "s_conv_b_f32", "s_dt_bias_f32",
+                                          "s_a_log_f32", "s_skip_f32", "s_norm_f32", "s_out", "l_in", "l_in_bias_f32",
+                                          "l_qnorm_f32", "l_knorm_f32", "l_out", "l_branch_norm_f32", "r_in", "r_decay_up",
+                                          "r_decay_bias_f32", "r_norm_f32", "r_out", "r_branch_norm_f32", "ff_in", "ff_out")]
+
+
+class SeqModelDesc(C.Structure):
+    """lcc_seq_model_desc"""
+    _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("dtype", C.c_int32),
+                ("eps", C.c_float), ("alpha", C.c_float), ("embed_scale", C.c_float), ("logit_softcap", C.c_float),
+                ("embed", C.c_void_p), ("inv_freq_f32", C.c_void_p), ("final_norm_f32", C.c_void_p), ("head", C.c_void_p),
+                ("layers", C.POINTER(SeqLayer))]
+
+
+class SeqEntry(C.Structure):
+    """lcc_seq_entry"""
+    _fields_ = [("n_new", C.c_int32), ("past", C.c_int32), ("ids", C.c_void_p), ("page_table", C.c_void_p),
+                ("scalars", C.c_void_p), ("layer_state", C.POINTER(C.c_void_p)), ("k_pages", C.POINTER(C.c_void_p)),
+                ("v_pages", C.POINTER(C.c_void_p))]
+
+
+DT_BF16, DT_F32 = 0, 1
+MIX_SSD, MIX_PARALLEL = 1, 2
+
+_libs = {}   # profile (None = the full library) -> CDLL
 
 
 def header_symbols() -> list[str]:
@@ -73,42 +104,63 @@ def header_symbols() -> list[str]:
     return sorted(set(re.findall(r"\b(lcc_[a-z0-9_]+)\s*\(", text)))
 
 
-def load_library(build_if_missing: bool = True) -> C.CDLL:
-    global _lib
-    if _lib is not None:
-        return _lib
-    if not LIB_PATH.exists():
-        if not build_if_missing:
-            raise LiveCCNativeError(f"{LIB_PATH} is missing (run `python -m livecc_b200.build`)")
-        from . import build as _build
+def _declare(lib: C.CDLL):
+    def sig(name, restype=None, argtypes=None):
+        fn = getattr(lib, name, None)   # a one-family library exports a subset of the header
+        if fn is None:
+            return
+        if restype is not None:
+            fn.restype = restype
+        if argtypes is not None:
+            fn.argtypes = argtypes
 
+    sig("lcc_create", C.c_void_p, [C.c_int])
+    sig("lcc_destroy", None, [C.c_void_p])
+    sig("lcc_last_error", C.c_char_p, [C.c_void_p])
+    sig("lcc_num_sms", None, [C.c_void_p])
+    sig("lcc_launch_count", C.c_uint64, [])
+    sig("lcc_model_create", C.c_void_p, [C.c_void_p, C.POINTER(ModelConfig), C.POINTER(ModelWeights)])
+    sig("lcc_model_destroy", None, [C.c_void_p])
+    sig("lcc_workspace_bytes", C.c_size_t, [C.c_void_p, C.c_int, C.c_int])
+    sig("lcc_ws_offset", C.c_size_t, [C.c_void_p, C.c_int])
+    sig("lcc_resize_aa_taps", None, [C.c_int, C.c_int])
+    sig("lcc_resize_aa_table", None, [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p])
+    sig("lcc_resize_plan_create", C.c_void_p, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int])
+    sig("lcc_resize_plan_destroy", None, [C.c_void_p])
+    sig("lcc_resize_plan_info", None, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int64)])
+    sig("lcc_seq_model_create", C.c_void_p, [C.c_void_p, C.POINTER(SeqModelDesc)])
+    sig("lcc_seq_model_destroy", None, [C.c_void_p])
+    sig("lcc_seq_workspace_bytes", C.c_size_t, [C.c_void_p, C.c_int, C.c_int])
+    sig("lcc_seq_bind_workspace", C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int])
+    sig("lcc_seq_layer_state_floats", C.c_int64, [C.c_void_p, C.c_int])
+    sig("lcc_seq_forward", C.c_int, [C.c_void_p, C.POINTER(SeqEntry), C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p,
+                                     C.c_void_p, C.c_void_p, C.c_void_p])
+
+
+def load_library(build_if_missing: bool = True, profile: str = None) -> C.CDLL:
+    """The full library serves every caller. A caller that names a `profile` (one model family's subset of the sources,
+    livecc_b200.build.PROFILES) gets the full library when it is there, and otherwise a library built from that subset
+    alone: serving one family compiles nothing else."""
+    if None in _libs:
+        return _libs[None]
+    if profile in _libs:
+        return _libs[profile]
+    from . import build as _build
+
+    use = None if (profile is None or LIB_PATH.exists()) else profile
+    path = _build.lib_path(use)
+    if use is not None:
+        _build.build(profile=use)       # cached by content hash: a no-op when the objects are current
+    elif not path.exists():
+        if not build_if_missing:
+            raise LiveCCNativeError(f"{path} is missing (run `python -m livecc_b200.build`)")
         _build.build()
-    lib = C.CDLL(str(LIB_PATH))
+    lib = C.CDLL(str(path))
     lib.lcc_abi_version.restype = C.c_int
     if lib.lcc_abi_version() != ABI_VERSION:
-        raise LiveCCNativeError("liblivecc_sm100a.so ABI version mismatch; rebuild it (python -m livecc_b200.build --force)")
-    lib.lcc_create.restype = C.c_void_p
-    lib.lcc_create.argtypes = [C.c_int]
-    lib.lcc_destroy.argtypes = [C.c_void_p]
-    lib.lcc_last_error.restype = C.c_char_p
-    lib.lcc_last_error.argtypes = [C.c_void_p]
-    lib.lcc_num_sms.argtypes = [C.c_void_p]
-    lib.lcc_launch_count.restype = C.c_uint64
-    lib.lcc_launch_count.argtypes = []
-    lib.lcc_model_create.restype = C.c_void_p
-    lib.lcc_model_create.argtypes = [C.c_void_p, C.POINTER(ModelConfig), C.POINTER(ModelWeights)]
-    lib.lcc_model_destroy.argtypes = [C.c_void_p]
-    lib.lcc_workspace_bytes.restype = C.c_size_t
-    lib.lcc_workspace_bytes.argtypes = [C.c_void_p, C.c_int, C.c_int]
-    lib.lcc_ws_offset.restype = C.c_size_t
-    lib.lcc_ws_offset.argtypes = [C.c_void_p, C.c_int]
-    lib.lcc_resize_aa_taps.argtypes = [C.c_int, C.c_int]
-    lib.lcc_resize_aa_table.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
-    lib.lcc_resize_plan_create.restype = C.c_void_p
-    lib.lcc_resize_plan_create.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
-    lib.lcc_resize_plan_destroy.argtypes = [C.c_void_p]
-    lib.lcc_resize_plan_info.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int64)]
-    _lib = lib
+        raise LiveCCNativeError(f"{path.name} ABI version mismatch; rebuild it (python -m livecc_b200.build --force)")
+    _declare(lib)
+    _libs[use] = lib
     return lib
 
 
@@ -149,8 +201,8 @@ def _i(x):
 class Context:
     """One lcc_ctx bound to one CUDA device."""
 
-    def __init__(self, device_index: int):
-        self.lib = load_library()
+    def __init__(self, device_index: int, profile: str = None):
+        self.lib = load_library(profile=profile)
         self.handle = self.lib.lcc_create(int(device_index))
         if not self.handle:
             raise LiveCCNativeError(
@@ -444,3 +496,47 @@ class NativeModel:
         arr = (StreamState * len(states))(*states)
         self._call("lcc_decode_mega_debug", arr, _i(len(states)), _i(layer_begin), _i(layer_end), _i(phase_mask),
                    _i(do_head), Context.stream_ptr())
+
+
+class SeqNativeModel:
+    """lcc_seq_model: layer list + weight pointers + bound workspace of a hybrid sequence model."""
+
+    def __init__(self, ctx: Context, desc: SeqModelDesc, keepalive):
+        self.ctx, self.lib = ctx, ctx.lib
+        self._keep = keepalive
+        self.handle = self.lib.lcc_seq_model_create(C.c_void_p(ctx.handle), C.byref(desc))
+        if not self.handle:
+            raise LiveCCNativeError(self.lib.lcc_last_error(C.c_void_p(ctx.handle)).decode())
+        self.n_layers = int(desc.n_layers)
+        self.workspace = None
+        self.cap_tokens = self.cap_want = 0
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.lcc_seq_model_destroy(C.c_void_p(self.handle))
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def state_floats(self):
+        return [int(self.lib.lcc_seq_layer_state_floats(C.c_void_p(self.handle), i)) for i in range(self.n_layers)]
+
+    def bind_workspace(self, max_tokens: int, max_want: int, device):
+        import torch
+
+        nbytes = self.lib.lcc_seq_workspace_bytes(C.c_void_p(self.handle), int(max_tokens), int(max_want))
+        self.workspace = torch.empty((nbytes,), dtype=torch.uint8, device=device)
+        self.ctx.check(self.lib.lcc_seq_bind_workspace(C.c_void_p(self.handle), _ptr(self.workspace), C.c_size_t(nbytes),
+                                                       int(max_tokens), int(max_want)), "lcc_seq_bind_workspace")
+        self.cap_tokens, self.cap_want = int(max_tokens), int(max_want)
+
+    def forward(self, entries, page_size, want_rows, n_want, logits, logits_copy=None, layer_dump=None):
+        """entries: list of SeqEntry (their pointer arrays must stay alive for the call)."""
+        arr = (SeqEntry * len(entries))(*entries)
+        rc = self.lib.lcc_seq_forward(C.c_void_p(self.handle), arr, len(entries), int(page_size), _ptr(want_rows), int(n_want),
+                                      _ptr(logits), _ptr(logits_copy), _ptr(layer_dump), Context.stream_ptr())
+        self.ctx.check(rc, "lcc_seq_forward")

@@ -18,6 +18,16 @@ CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "liblivecc_sm100a.so"
 OBJ_DIR = PKG_DIR / "build"
 
+# A profile is the subset of csrc/*.cu one model family needs; it links into a library of its own, so that serving that
+# family alone compiles nothing else. The full library (profile None) holds every source and exports a superset.
+PROFILES = {
+    "seq": ["cabi_core", "gemm_tcgen05", "sampling", "linear_any", "recurrent", "attn_local", "rowops", "seq_model"],
+}
+
+
+def lib_path(profile: str | None = None) -> Path:
+    return LIB_PATH if profile is None else PKG_DIR / f"liblivecc_{profile}_sm100a.so"
+
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
@@ -33,8 +43,10 @@ def _nvcc() -> str:
     return nvcc
 
 
-def _sources() -> list[Path]:
-    return sorted(CSRC.glob("*.cu"))
+def _sources(profile: str | None = None) -> list[Path]:
+    if profile is None:
+        return sorted(CSRC.glob("*.cu"))
+    return [CSRC / f"{name}.cu" for name in PROFILES[profile]]
 
 
 def _fingerprint(src: Path) -> str:
@@ -46,13 +58,14 @@ def _fingerprint(src: Path) -> str:
     return h.hexdigest()
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile every csrc/*.cu to an object (cached by content hash) and link the shared library."""
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, profile: str | None = None) -> Path:
+    """Compile csrc/*.cu (all of them, or one profile's subset) to objects cached by content hash and link the library."""
     nvcc = _nvcc()
     OBJ_DIR.mkdir(exist_ok=True)
+    out_path = lib_path(profile)
     objs: list[Path] = []
     jobs = []
-    for src in _sources():
+    for src in _sources(profile):
         obj = OBJ_DIR / (src.stem + ".o")
         stamp = OBJ_DIR / (src.stem + ".sha")
         fp = _fingerprint(src)
@@ -78,14 +91,18 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(run, jobs))
-    if jobs or not LIB_PATH.exists() or force:
-        cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-lcudart"]
+    stale = not out_path.exists() or any(o.stat().st_mtime > out_path.stat().st_mtime for o in objs)
+    if jobs or stale or force:
+        tmp = out_path.with_suffix(f".tmp{os.getpid()}")
+        cmd = [nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-lcudart"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB_PATH
+        os.replace(tmp, out_path)
+    return out_path
 
 
 if __name__ == "__main__":
-    p = build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv)
+    prof = next((a.split("=", 1)[1] for a in sys.argv if a.startswith("--profile=")), None)
+    p = build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv, profile=prof)
     print(p)

@@ -248,18 +248,134 @@ def canonical_hf_name(name: str) -> str:
 
 def iter_hf_checkpoint(model_path: str) -> Iterator[Tuple[str, torch.Tensor]]:
     """Streams (canonical_name, tensor) from every *.safetensors file of a checkpoint directory."""
+    for name, t in iter_safetensors(model_path):
+        yield canonical_hf_name(name), t
+
+
+_ST_DTYPES = {"BF16": torch.bfloat16, "F16": torch.float16, "F32": torch.float32, "F64": torch.float64,
+              "I64": torch.int64, "I32": torch.int32, "I16": torch.int16, "I8": torch.int8, "U8": torch.uint8, "BOOL": torch.bool}
+
+
+def read_safetensors(path: str) -> Iterator[Tuple[str, torch.Tensor]]:
+    """(name, tensor) of one .safetensors file, read without the safetensors package: an 8-byte little-endian header length,
+    that many bytes of JSON (name -> dtype, shape, data_offsets), then the data."""
+    import json
+    import struct
+
+    import numpy as np
+
+    with open(path, "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        meta = json.loads(f.read(n))
+    data = np.memmap(path, dtype=np.uint8, mode="r", offset=8 + n)
+    for name, info in meta.items():
+        if name == "__metadata__":
+            continue
+        if info["dtype"] not in _ST_DTYPES:
+            raise NotImplementedError(f"{path}: tensor {name!r} has dtype {info['dtype']}")
+        a, b = info["data_offsets"]
+        raw = torch.from_numpy(np.array(data[a:b]))            # a private copy: the memmap is read-only
+        yield name, raw.view(_ST_DTYPES[info["dtype"]]).reshape(info["shape"])
+
+
+def iter_safetensors(model_path: str) -> Iterator[Tuple[str, torch.Tensor]]:
+    """Streams (name, tensor) from every *.safetensors file of a checkpoint directory, names as stored."""
     import glob
     import os
-
-    from safetensors import safe_open
 
     files = sorted(glob.glob(os.path.join(model_path, "*.safetensors")))
     if not files:
         raise FileNotFoundError(f"no *.safetensors under {model_path!r} (checkpoints cannot be downloaded offline)")
     for f in files:
-        with safe_open(f, framework="pt") as sf:
-            for name in sf.keys():
-                yield canonical_hf_name(name), sf.get_tensor(name)
+        yield from read_safetensors(f)
+
+
+def write_safetensors(path: str, tensors: Dict[str, torch.Tensor]) -> None:
+    """The inverse of read_safetensors (synthetic checkpoints on disk for tests and benchmarks)."""
+    import json
+    import struct
+
+    names = {v: k for k, v in _ST_DTYPES.items()}
+    meta, blobs, off = {}, [], 0
+    for name, t in tensors.items():
+        b = t.detach().cpu().contiguous().view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        meta[name] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(b)]}
+        blobs.append(b)
+        off += len(b)
+    head = json.dumps(meta, separators=(",", ":")).encode()
+    head += b" " * (-len(head) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(head)))
+        f.write(head)
+        for b in blobs:
+            f.write(b)
+
+
+def seq_param_specs(cfg) -> List[Tuple[str, Tuple[int, ...], str]]:
+    """(name, shape, kind) of every tensor of a hybrid sequence model (config.SeqModelConfig); kind picks the synthetic
+    fill: 'w' matrix, 'b' bias, 'norm' norm weight, 'conv' taps, 'dt' step bias, 'alog' log decay rate, 'skip'."""
+    W = cfg.width
+    specs = [("embed", (cfg.vocab, W), "embed")]
+    for i, L in enumerate(cfg.layers):
+        p = f"l{i}."
+        specs.append((p + "norm1", (W,), "norm"))
+        if L.ff:
+            specs.append((p + "norm2", (W,), "norm"))
+        if L.type == "mamba2":
+            s, m = L.ssd, p + "mix."
+            specs += [(m + "in", (s.proj_rows, W), "w"), (m + "conv", (s.conv_channels, s.conv), "conv"),
+                      (m + "conv.b", (s.conv_channels,), "b"), (m + "dt_bias", (s.heads,), "dt"), (m + "A_log", (s.heads,), "alog"),
+                      (m + "D", (s.heads,), "skip"), (m + "norm", (s.inner,), "norm"), (m + "o", (W, s.inner), "w")]
+        else:
+            l, r = L.left, L.right
+            a, b = p + "mix.left.", p + "mix.right."
+            rank = r.rank or max(4, r.dim // 2)
+            specs += [(a + "q", (l.heads * l.dim, W), "w"), (a + "q.b", (l.heads * l.dim,), "b"),
+                      (a + "k", (l.kv_heads * l.dim, W), "w"), (a + "k.b", (l.kv_heads * l.dim,), "b"),
+                      (a + "v", (l.kv_heads * l.vdim, W), "w"), (a + "v.b", (l.kv_heads * l.vdim,), "b"),
+                      (a + "q.norm", (l.heads * l.dim,), "norm"), (a + "k.norm", (l.kv_heads * l.dim,), "norm"),
+                      (a + "g", (l.heads, W), "w"), (a + "o", (W, l.heads * l.vdim), "w"),
+                      (b + "q", (r.heads * r.dim, W), "w"), (b + "k", (r.heads * r.dim, W), "w"),
+                      (b + "v", (r.heads * r.vdim, W), "w"), (b + "g", (r.heads * r.vdim, W), "w"),
+                      (b + "o", (W, r.heads * r.vdim), "w"), (b + "norm", (r.vdim,), "norm"), (b + "a1", (rank, W), "w"),
+                      (b + "a2", (r.heads * r.dim, rank), "w"), (b + "a2.b", (r.heads * r.dim,), "decay_b"),
+                      (a + "out", (W,), "norm"), (b + "out", (W,), "norm")]
+        if L.ff:
+            specs += [(p + "mlp.gate", (L.ff, W), "w"), (p + "mlp.up", (L.ff, W), "w"), (p + "mlp.down", (W, L.ff), "w")]
+    specs += [("final.norm", (W,), "norm"), ("head", (cfg.vocab, W), "w")]
+    return specs
+
+
+def synthetic_seq_tensors(cfg, seed: int = 1234, device="cpu") -> Dict[str, torch.Tensor]:
+    """Random bf16 checkpoint of a hybrid sequence model (counter-hash fill, identical on every device). Matrices have
+    unit-variance rows scaled by 1/sqrt(fan-in); decay rates and step biases are spread so that both fast and slow
+    heads occur."""
+    out = {}
+    for idx, (name, shape, kind) in enumerate(seq_param_specs(cfg)):
+        n = 1
+        for d in shape:
+            n *= d
+        u = hash_uniform(n, seed * 1000003 + idx, device).reshape(shape)   # [-0.5, 0.5)
+        if kind == "w":
+            t = u * (3.4641 / (shape[-1] ** 0.5))
+        elif kind == "embed":
+            t = u * 3.4641
+        elif kind == "norm":
+            t = 1.0 + 0.5 * u
+        elif kind == "conv":
+            t = u * 1.5
+        elif kind == "dt":
+            t = u * 4.0 - 2.0
+        elif kind == "alog":
+            t = u * 3.0
+        elif kind == "skip":
+            t = 1.0 + u
+        elif kind == "decay_b":
+            t = 2.0 + 4.0 * u
+        else:
+            t = u * 0.5
+        out[name] = t.to(torch.bfloat16)
+    return out
 
 
 # --------------------------------------------------------------------------------------------

@@ -121,3 +121,130 @@ class LiveCCConfig:
             raise ValueError("merger output must equal text hidden size")
         if t.intermediate_size % 32 or t.hidden_size % 8 or v.embed_dim % 8:
             raise ValueError("unsupported dims")
+
+
+# ------------------------------------------------------------------------------------------------
+# Hybrid sequence models (decoder-only language models built from recurrent and local-attention mixers)
+# ------------------------------------------------------------------------------------------------
+@dataclass
+class SsdMixerConfig:
+    """Scalar-decay state-space mixer: heads x vdim value channels, `state` key channels shared by heads/groups heads."""
+    heads: int
+    vdim: int
+    state: int
+    groups: int = 1
+    conv: int = 4
+    norm_groups: int = 1
+
+    @property
+    def inner(self) -> int:
+        return self.heads * self.vdim
+
+    @property
+    def conv_channels(self) -> int:
+        return self.inner + 2 * self.groups * self.state
+
+    @property
+    def proj_rows(self) -> int:
+        return self.inner + self.conv_channels + self.heads
+
+
+@dataclass
+class ChunkAttnConfig:
+    """Attention inside chunks of `chunk` positions (0 = plain causal) with a softmax sink and a per-head output gate."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    chunk: int
+    scale: float
+
+
+@dataclass
+class GlaConfig:
+    """Gated linear attention with per-key-channel decays sigmoid(z)^(1/tau); z comes through a rank-`rank` bottleneck."""
+    heads: int
+    dim: int
+    vdim: int
+    tau: float
+    rank: int = 0   # read from the tensor shapes when 0
+
+
+@dataclass
+class SeqLayerConfig:
+    type: str                      # "mamba2" | "parallel"
+    ssd: SsdMixerConfig = None
+    left: ChunkAttnConfig = None
+    right: GlaConfig = None
+    ff: int = 0                    # 0 = the layer has no feed-forward
+
+
+@dataclass
+class SeqModelConfig:
+    architecture: str
+    vocab: int
+    width: int
+    layers: list
+    eps: float = 1e-5
+    alpha: float = 1.0
+    embed_scale: float = 1.0
+    logit_softcap: float = 0.0
+    eos_token_id: int = -1         # none unless config.json names one
+
+    @staticmethod
+    def from_json(d: dict) -> "SeqModelConfig":
+        """config.json of a hybrid sequence model: `layers` lists each layer's `type`, its mixer's sizes and its `mlp`."""
+        layers = []
+        for i, L in enumerate(d["layers"]):
+            mx, mlp = L["mixer"], L.get("mlp")
+            ff = 0
+            if mlp is not None:
+                if mlp.get("kind", "dense") != "dense":
+                    raise NotImplementedError(f"layer {i}: feed-forward kind {mlp.get('kind')!r} is not supported")
+                ff = int(mlp["ff"])
+            if L["type"] == "mamba2":
+                layers.append(SeqLayerConfig("mamba2", ssd=SsdMixerConfig(
+                    heads=int(mx["heads"]), vdim=int(mx["vdim"]), state=int(mx["state"]), groups=int(mx.get("groups", 1)),
+                    conv=int(mx.get("conv", 4)), norm_groups=int(mx.get("norm_groups", 1))), ff=ff))
+            elif L["type"] == "parallel":
+                l, r = mx["left"], mx["right"]
+                left = ChunkAttnConfig(heads=int(l["heads"]), kv_heads=int(l.get("kv_heads", l["heads"])), dim=int(l["dim"]),
+                                       vdim=int(l.get("vdim", l["dim"])), chunk=int((l.get("mask") or {}).get("size", 0)),
+                                       scale=float(l.get("scale", float(l["dim"]) ** -0.5)))
+                right = GlaConfig(heads=int(r["heads"]), dim=int(r["dim"]), vdim=int(r.get("vdim", r["dim"])),
+                                  tau=float(r.get("tau", 1.0)))
+                layers.append(SeqLayerConfig("parallel", left=left, right=right, ff=ff))
+            else:
+                raise NotImplementedError(f"layer {i}: mixer type {L['type']!r} is not supported")
+        return SeqModelConfig(
+            architecture=d.get("architecture", "Bimopel"), vocab=int(d["vocab"]), width=int(d["width"]), layers=layers,
+            eps=float((d.get("norm") or {}).get("eps", 1e-5)), alpha=float(d.get("postln_alpha", 1.0)),
+            embed_scale=float((d.get("embedding") or {}).get("scale", 1.0)), logit_softcap=float(d.get("logit_softcap") or 0.0),
+            eos_token_id=int(d.get("eos_token_id", -1)))
+
+    def to_json(self) -> dict:
+        """The inverse of from_json (used to write synthetic checkpoints)."""
+        out = []
+        for L in self.layers:
+            if L.type == "mamba2":
+                s = L.ssd
+                mx = dict(heads=s.heads, vdim=s.vdim, state=s.state, groups=s.groups, conv=s.conv, norm_groups=s.norm_groups)
+            else:
+                l, r = L.left, L.right
+                mx = dict(left=dict(heads=l.heads, kv_heads=l.kv_heads, dim=l.dim, vdim=l.vdim, mask=dict(size=l.chunk), scale=l.scale),
+                          right=dict(heads=r.heads, dim=r.dim, vdim=r.vdim, tau=r.tau))
+            out.append(dict(type=L.type, mixer=mx, mlp=dict(ff=L.ff, kind="dense") if L.ff else None))
+        return dict(architecture=self.architecture, vocab=self.vocab, width=self.width, layers=out, norm=dict(eps=self.eps),
+                    postln_alpha=self.alpha, embedding=dict(scale=self.embed_scale), logit_softcap=self.logit_softcap)
+
+    def validate(self) -> None:
+        if self.width < 2 or self.width % 2:
+            raise ValueError("the sinusoidal position vector needs an even width")
+        for i, L in enumerate(self.layers):
+            if L.type == "mamba2":
+                s = L.ssd
+                if s.heads % s.groups or s.inner % s.norm_groups or not 1 <= s.conv <= 8 or s.state > 512:
+                    raise ValueError(f"layer {i}: unsupported state-space sizes {s}")
+            else:
+                if L.left.heads % L.left.kv_heads or L.right.dim > 512:
+                    raise ValueError(f"layer {i}: unsupported attention sizes")

@@ -1,0 +1,118 @@
+// General-shape linear layers: C[M,N] = A[M,K] x W[N,K]^T (+ bias), fp32 accumulation, bf16 or fp32 storage.
+// Two CUDA-core kernels cover every shape the tensor-core GEMM (gemm_tcgen05.cu) does not take: ragged N or K, fp32
+// storage (true fp32 FMAs, no reduced-precision matrix mode), and the few-row case of a decode step, where the
+// weight matrix is streamed once and every row of A is multiplied against it (HBM-bound).
+#include "common.cuh"
+#include "launch.h"
+#include "seqmix.h"
+
+namespace lcc {
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+constexpr int BM = 64, BN = 64, BK = 16;
+
+// 64 x 64 output tile per CTA, 256 threads x (4 x 4) accumulators, k-slices of 16 staged in shared memory as fp32.
+template <typename T, typename TC>
+__global__ void __launch_bounds__(256) linear_tile_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int ldw,
+                                                          const float* __restrict__ bias, TC* __restrict__ C, int ldc, int M,
+                                                          int N, int K) {
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int tm = (tid / 16) * 4, tn = (tid % 16) * 4;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        // 64 rows x 16 k per operand = 1024 elements, 4 per thread; consecutive threads read consecutive k (coalesced)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int e = tid + i * 256, r = e / BK, k = e % BK;
+            const int gm = m0 + r, gn = n0 + r, gk = k0 + k;
+            As[k][r] = (gm < M && gk < K) ? ldf(A + (size_t)gm * lda + gk) : 0.f;
+            Ws[k][r] = (gn < N && gk < K) ? ldf(W + (size_t)gn * ldw + gk) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float a[4], w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { a[i] = As[k][tm + i]; w[i] = Ws[k][tn + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int gm = m0 + tm + i;
+        if (gm >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + tn + j;
+            if (gn < N) stf(C + (size_t)gm * ldc + gn, acc[i][j] + (bias ? bias[gn] : 0.f));
+        }
+    }
+}
+
+// Few rows (M <= 8): one warp per output column streams that row of W once; lanes stride over k.
+constexpr int kRowsMax = 8;
+template <typename T, typename TC>
+__global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int ldw,
+                                                          const float* __restrict__ bias, TC* __restrict__ C, int ldc, int M,
+                                                          int N, int K) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + warp;
+    if (n >= N) return;
+    const T* w = W + (size_t)n * ldw;
+    float acc[kRowsMax];
+#pragma unroll
+    for (int m = 0; m < kRowsMax; ++m) acc[m] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+        const float wv = ldf(w + k);
+#pragma unroll
+        for (int m = 0; m < kRowsMax; ++m)
+            if (m < M) acc[m] = fmaf(ldf(A + (size_t)m * lda + k), wv, acc[m]);
+    }
+#pragma unroll
+    for (int m = 0; m < kRowsMax; ++m) {
+        if (m < M) {
+            const float v = warp_sum(acc[m]);
+            if (lane == 0) stf(C + (size_t)m * ldc + n, v + (bias ? bias[n] : 0.f));
+        }
+    }
+}
+
+template <typename T, typename TC>
+int launch_linear(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N, int K,
+                  cudaStream_t s) {
+    if (M <= kRowsMax) {
+        count_launch();
+        linear_rows_kernel<T, TC><<<(N + 7) / 8, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K);
+    } else {
+        dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+        count_launch();
+        linear_tile_kernel<T, TC><<<grid, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K);
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+}  // namespace
+
+int linear_any(int dt, const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, bool c_f32,
+               int M, int N, int K, cudaStream_t s) {
+    if (!A || !W || !C || M < 1 || N < 1 || K < 1 || lda < K || ldw < K || ldc < N) return -2;
+    if (dt == DT_F32) return launch_linear<float, float>(A, lda, W, ldw, bias, C, ldc, M, N, K, s);
+    if (c_f32) return launch_linear<bf16, float>(A, lda, W, ldw, bias, C, ldc, M, N, K, s);
+    return launch_linear<bf16, bf16>(A, lda, W, ldw, bias, C, ldc, M, N, K, s);
+}
+
+}  // namespace lcc

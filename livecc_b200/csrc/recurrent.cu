@@ -1,0 +1,245 @@
+// Recurrent sequence mixers with state carried from call to call (prefill portions and decode steps run the same
+// kernels): the short causal convolution of a state-space layer, its step sizes and decays, the per-channel decays of
+// gated linear attention, and the gated linear recurrence both share:
+//     St <- diag(a_t) St + k_t (sc_t u_t)^T ,  y_t = St^T c_t + skip * u_t          (St: N x P per head, fp32)
+// Everything that enters the recurrence is fp32; the projections it reads are in the model's storage type.
+#include <math.h>
+
+#include "../../include/livecc_b200.h"
+#include "common.cuh"
+#include "launch.h"
+#include "seqmix.h"
+
+namespace lcc {
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ bool seq_done(const SeqPos& p) { return p.finished && *p.finished; }
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+
+// ---- causal convolution -----------------------------------------------------------------------------------------------
+constexpr int kMaxTaps = 8;
+
+// out[t, c] = silu(b[c] + sum_j w[c, j] * in[t - (taps-1) + j, c]); rows before 0 come from the carry.
+template <typename T>
+__global__ void causal_conv_silu_kernel(const T* __restrict__ in, int ld_in, T* __restrict__ out, int ld_out,
+                                        const float* __restrict__ w, const float* __restrict__ b,
+                                        const float* __restrict__ carry, int S, int C, int taps, SeqPos pos) {
+    if (seq_done(pos)) return;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t = blockIdx.y;
+    if (c >= C) return;
+    float acc = b[c];
+    for (int j = 0; j < taps; ++j) {
+        const int tt = t - (taps - 1) + j;
+        const float v = tt >= 0 ? ldf(in + (size_t)tt * ld_in + c) : carry[(size_t)c * (taps - 1) + (taps - 1 + tt)];
+        acc = fmaf(w[(size_t)c * taps + j], v, acc);
+    }
+    stf(out + (size_t)t * ld_out + c, silu_f(acc));
+}
+
+// carry[c, i] <- input at row S - (taps-1) + i (an older carry entry when that row is negative)
+template <typename T>
+__global__ void conv_carry_update_kernel(const T* __restrict__ in, int ld_in, float* __restrict__ carry, int S, int C,
+                                         int taps, SeqPos pos) {
+    if (seq_done(pos)) return;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int n = taps - 1;
+    float nv[kMaxTaps];
+    for (int i = 0; i < n; ++i) {
+        const int tt = S - n + i;
+        nv[i] = tt >= 0 ? ldf(in + (size_t)tt * ld_in + c) : carry[(size_t)c * n + (n + tt)];
+    }
+    for (int i = 0; i < n; ++i) carry[(size_t)c * n + i] = nv[i];
+}
+
+// ---- step sizes and decays ----------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void ssm_step_decay_kernel(const T* __restrict__ raw, int ld, const float* __restrict__ dt_bias,
+                                      const float* __restrict__ a_log, float* __restrict__ dt_out,
+                                      float* __restrict__ decay_out, int S, int heads) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= S * heads) return;
+    const int t = i / heads, h = i % heads;
+    const float dt = softplus_f(ldf(raw + (size_t)t * ld + h) + dt_bias[h]);
+    dt_out[i] = dt;
+    decay_out[i] = expf(-expf(a_log[h]) * dt);
+}
+
+template <typename T>
+__global__ void gla_decay_kernel(const T* __restrict__ z, int ld, const float* __restrict__ bias, float inv_tau,
+                                 float* __restrict__ decay_out, int S, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= S * n) return;
+    const int t = i / n, c = i % n;
+    const float x = ldf(z + (size_t)t * ld + c) + (bias ? bias[c] : 0.f);
+    // log(sigmoid(x)) = min(x, 0) - log1p(exp(-|x|)); the decay is its exponential scaled by 1/tau
+    const float ls = fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
+    decay_out[i] = expf(ls * inv_tau);
+}
+
+// ---- gated linear recurrence --------------------------------------------------------------------------------------------
+// A thread keeps NT = 16 state entries St[n0..n0+15, p] of one value channel p in registers; JP (a power of two >= N / 16)
+// neighbouring lanes share p and reduce y with shuffles. Tokens are staged through shared memory TT at a time so that the
+// sequential loop over tokens reads only registers and shared memory and has no block barrier.
+constexpr int NT = 16;
+constexpr int TT = 16;
+constexpr int kScanThreads = 128;
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kScanThreads) gated_scan_kernel(ScanArgs a, SeqPos pos) {
+    if (seq_done(pos)) return;
+    extern __shared__ float sm[];
+    const int N = a.N, P = a.P, S = a.S;
+    const int JP = blockDim.x;                 // lanes per value channel (x fastest: they sit in one warp)
+    const int cols = blockDim.y;               // value channels per CTA
+    const int h = blockIdx.x;
+    const int col = threadIdx.y;
+    const int p = blockIdx.y * cols + col;
+    const int j = threadIdx.x;
+    const int tid = threadIdx.y * JP + threadIdx.x, nthr = cols * JP;
+    const int n0 = j * NT;
+    const int g = h / a.heads_per_group;
+    // shared: k[TT][N], c[TT][N], dec[TT][VEC ? N : 1], sc[TT], u[TT][cols]
+    float* sk = sm;
+    float* scv = sk + TT * N;
+    float* sd = scv + TT * N;
+    float* ssc = sd + TT * (VEC ? N : 1);
+    float* su = ssc + TT;
+
+    float st[NT];
+    float* gstate = a.state + ((size_t)h * P + (p < P ? p : 0)) * N;
+#pragma unroll
+    for (int i = 0; i < NT; ++i) st[i] = (p < P && n0 + i < N) ? gstate[n0 + i] : 0.f;
+    const float skip = a.skip ? a.skip[h] : 0.f;
+    const T* gk = (const T*)a.k + (size_t)g * N;
+    const T* gc = (const T*)a.c + (size_t)g * N;
+    const T* gu = (const T*)a.u + (size_t)h * P + blockIdx.y * cols;
+
+    for (int t0 = 0; t0 < S; t0 += TT) {
+        const int nt = min(TT, S - t0);
+        __syncthreads();
+        for (int e = tid; e < nt * N; e += nthr) {
+            const int t = e / N, n = e % N;
+            sk[e] = ldf(gk + (size_t)(t0 + t) * a.ld_k + n);
+            scv[e] = ldf(gc + (size_t)(t0 + t) * a.ld_c + n) * a.cs;
+            if (VEC) sd[e] = a.a[((size_t)(t0 + t) * a.heads + h) * N + n];
+        }
+        for (int e = tid; e < nt; e += nthr) {
+            if (!VEC) sd[e] = a.a[(size_t)(t0 + e) * a.heads + h];
+            ssc[e] = a.sc ? a.sc[(size_t)(t0 + e) * a.heads + h] : 1.f;
+        }
+        for (int e = tid; e < nt * cols; e += nthr) {
+            const int t = e / cols, c = e % cols;
+            su[e] = (blockIdx.y * cols + c < P) ? ldf(gu + (size_t)(t0 + t) * a.ld_u + c) : 0.f;
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            const float u = su[t * cols + col];
+            const float su_t = ssc[t] * u;
+            const float* kt = sk + t * N + n0;
+            const float* ct = scv + t * N + n0;
+            const float* dv = sd + (VEC ? t * N + n0 : t);
+            float y = 0.f;
+#pragma unroll
+            for (int i = 0; i < NT; ++i) {
+                if (n0 + i < N) {
+                    const float d = VEC ? dv[i] : dv[0];
+                    st[i] = fmaf(d, st[i], kt[i] * su_t);
+                    y = fmaf(st[i], ct[i], y);
+                }
+            }
+            for (int o = JP >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);   // fixed butterfly order
+            if (j == 0 && p < P) a.y[(size_t)(t0 + t) * a.ld_y + (size_t)h * P + p] = y + skip * u;
+        }
+    }
+    if (p < P) {
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+            if (n0 + i < N) gstate[n0 + i] = st[i];
+    }
+}
+
+}  // namespace
+
+int causal_conv_silu(int dt, const void* in, int ld_in, void* out, int ld_out, const float* w, const float* b,
+                     float* carry, int S, int C, int taps, SeqPos pos, cudaStream_t s) {
+    if (!in || !out || !w || !b || !carry || S < 1 || C < 1 || taps < 1 || taps > kMaxTaps) return -2;
+    dim3 grid((C + 127) / 128, S);
+    count_launch();
+    if (dt == DT_F32)
+        causal_conv_silu_kernel<float><<<grid, 128, 0, s>>>((const float*)in, ld_in, (float*)out, ld_out, w, b, carry, S, C, taps, pos);
+    else
+        causal_conv_silu_kernel<bf16><<<grid, 128, 0, s>>>((const bf16*)in, ld_in, (bf16*)out, ld_out, w, b, carry, S, C, taps, pos);
+    if (taps > 1) {
+        count_launch();
+        if (dt == DT_F32)
+            conv_carry_update_kernel<float><<<(C + 127) / 128, 128, 0, s>>>((const float*)in, ld_in, carry, S, C, taps, pos);
+        else
+            conv_carry_update_kernel<bf16><<<(C + 127) / 128, 128, 0, s>>>((const bf16*)in, ld_in, carry, S, C, taps, pos);
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+int ssm_step_decay(int dt, const void* raw, int ld, const float* dt_bias, const float* a_log, float* dt_out,
+                   float* decay_out, int S, int heads, cudaStream_t s) {
+    if (!raw || !dt_bias || !a_log || !dt_out || !decay_out || S < 1 || heads < 1) return -2;
+    const int n = S * heads;
+    count_launch();
+    if (dt == DT_F32)
+        ssm_step_decay_kernel<float><<<(n + 255) / 256, 256, 0, s>>>((const float*)raw, ld, dt_bias, a_log, dt_out, decay_out, S, heads);
+    else
+        ssm_step_decay_kernel<bf16><<<(n + 255) / 256, 256, 0, s>>>((const bf16*)raw, ld, dt_bias, a_log, dt_out, decay_out, S, heads);
+    return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+int gla_decay(int dt, const void* z, int ld, const float* bias, float tau, float* decay_out, int S, int n,
+              cudaStream_t s) {
+    if (!z || !decay_out || S < 1 || n < 1 || !(tau > 0.f)) return -2;
+    const int tot = S * n;
+    count_launch();
+    if (dt == DT_F32)
+        gla_decay_kernel<float><<<(tot + 255) / 256, 256, 0, s>>>((const float*)z, ld, bias, 1.f / tau, decay_out, S, n);
+    else
+        gla_decay_kernel<bf16><<<(tot + 255) / 256, 256, 0, s>>>((const bf16*)z, ld, bias, 1.f / tau, decay_out, S, n);
+    return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+int gated_scan(const ScanArgs& a, SeqPos pos, cudaStream_t s) {
+    if (!a.k || !a.c || !a.u || !a.a || !a.state || !a.y || a.S < 1 || a.heads < 1 || a.N < 1 || a.P < 1 ||
+        a.heads_per_group < 1)
+        return -2;
+    int JP = 1;
+    while (JP * NT < a.N) JP *= 2;
+    if (JP > 32) return -3;  // N <= 512
+    int cols = kScanThreads / JP;
+    while (cols * JP > 32 && cols / 2 >= a.P) cols /= 2;   // narrow heads: fewer idle lanes, but always whole warps
+    dim3 block(JP, cols), grid(a.heads, (a.P + cols - 1) / cols);
+    const size_t smem = sizeof(float) * ((size_t)TT * a.N * 2 + (size_t)TT * (a.vec_decay ? a.N : 1) + TT +
+                                         (size_t)TT * cols);
+    if (smem > 200 * 1024) return -3;
+    count_launch();
+#define LCC_SCAN(T, V)                                                                                            \
+    do {                                                                                                          \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(gated_scan_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        gated_scan_kernel<T, V><<<grid, block, smem, s>>>(a, pos);                                                \
+    } while (0)
+    if (a.dt == DT_F32) {
+        if (a.vec_decay) LCC_SCAN(float, true); else LCC_SCAN(float, false);
+    } else {
+        if (a.vec_decay) LCC_SCAN(bf16, true); else LCC_SCAN(bf16, false);
+    }
+#undef LCC_SCAN
+    return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+}  // namespace lcc

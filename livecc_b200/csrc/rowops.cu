@@ -1,0 +1,203 @@
+// Row-wise ops of the hybrid decoder models. The residual stream, every norm and every sum of squares is fp32; `xa` /
+// `out` copies in the model's storage type feed the next linear layer.
+#include <math.h>
+
+#include "common.cuh"
+#include "launch.h"
+#include "seqmix.h"
+
+namespace lcc {
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ int seq_past(const SeqPos& p, int) { return p.kv_len ? *p.kv_len : p.past; }
+__device__ __forceinline__ bool seq_done(const SeqPos& p) { return p.finished && *p.finished; }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+
+template <typename T>
+__global__ void embed_sinusoid_kernel(const int64_t* __restrict__ ids, const int* __restrict__ seq_len, const T* __restrict__ table,
+                                      int64_t vocab, float scale, const float* __restrict__ inv_freq, float* __restrict__ x32,
+                                      T* __restrict__ xa, int S, int W, SeqPos pos) {
+    if (seq_done(pos)) return;
+    const int r = blockIdx.x;
+    const int64_t id = seq_len ? ids[*seq_len - S + r] : ids[r];
+    const float p = (float)(seq_past(pos, S) + r);
+    const bool ok = id >= 0 && id < vocab;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float ang = p * inv_freq[c >> 1];
+        const float pe = (c & 1) ? cosf(ang) : sinf(ang);
+        const float v = (ok ? ldf(table + (size_t)id * W + c) * scale : 0.f) + pe;
+        x32[(size_t)r * W + c] = v;
+        stf(xa + (size_t)r * W + c, v);
+    }
+}
+
+// One CTA per row; three passes over the row (the operands stay in L1/L2).
+template <typename T>
+__global__ void __launch_bounds__(256) postnorm_residual_kernel(float* __restrict__ x32, T* __restrict__ xa, const T* __restrict__ a,
+                                                                int ld_a, const float* __restrict__ wa, const T* __restrict__ b,
+                                                                int ld_b, const float* __restrict__ wb, const float* __restrict__ w,
+                                                                float alpha, float eps, int W) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    float* x = x32 + (size_t)r * W;
+    const T* ar = a + (size_t)r * ld_a;
+    const T* br = b ? b + (size_t)r * ld_b : nullptr;
+    float ra = 1.f, rb = 1.f;
+    if (br) {
+        float sa = 0.f, sb = 0.f;
+        for (int c = threadIdx.x; c < W; c += blockDim.x) {
+            const float va = ldf(ar + c), vb = ldf(br + c);
+            sa = fmaf(va, va, sa);
+            sb = fmaf(vb, vb, sb);
+        }
+        sa = block_sum(sa, red);
+        sb = block_sum(sb, red);
+        ra = 1.f / sqrtf(sa / (float)W + eps);
+        rb = 1.f / sqrtf(sb / (float)W + eps);
+    }
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float m = br ? 0.5f * (ldf(ar + c) * ra * wa[c] + ldf(br + c) * rb * wb[c]) : ldf(ar + c);
+        const float v = fmaf(alpha, x[c], m);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float rn = 1.f / sqrtf(ss / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float m = br ? 0.5f * (ldf(ar + c) * ra * wa[c] + ldf(br + c) * rb * wb[c]) : ldf(ar + c);
+        const float v = fmaf(alpha, x[c], m) * rn * w[c];
+        x[c] = v;
+        stf(xa + (size_t)r * W + c, v);
+    }
+}
+
+// One warp per (row, group).
+template <typename T>
+__global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __restrict__ y, int ld_y, const T* __restrict__ gate,
+                                                               int ld_gate, const float* __restrict__ w, int w_len, T* __restrict__ out,
+                                                               int ld_out, int S, int n, int group, int gate_first, float eps) {
+    const int ngroups = n / group;
+    const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (wid >= S * ngroups) return;
+    const int r = wid / ngroups, c0 = (wid % ngroups) * group;
+    const float* yr = y + (size_t)r * ld_y + c0;
+    const T* gr = gate + (size_t)r * ld_gate + c0;
+    float ss = 0.f;
+    for (int c = lane; c < group; c += 32) {
+        const float v = gate_first ? yr[c] * silu_f(ldf(gr + c)) : yr[c];
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float rn = 1.f / sqrtf(ss / (float)group + eps);
+    for (int c = lane; c < group; c += 32) {
+        const float gsl = silu_f(ldf(gr + c));
+        const float wv = w[(c0 + c) % w_len];
+        const float v = gate_first ? yr[c] * gsl * rn * wv : yr[c] * rn * wv * gsl;
+        stf(out + (size_t)r * ld_out + c0 + c, v);
+    }
+}
+
+template <typename T>
+__global__ void glu_gelu_tanh_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int ld_out, int S, int F) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)S * F) return;
+    const int r = (int)(i / F), c = (int)(i % F);
+    const float z = ldf(gu + (size_t)r * ld + c), u = ldf(gu + (size_t)r * ld + F + c);
+    const float act = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    stf(out + (size_t)r * ld_out + c, act * u);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) gather_rmsnorm_kernel(const float* __restrict__ x32, const int* __restrict__ rows,
+                                                             const float* __restrict__ w, float eps, T* __restrict__ out, int W) {
+    __shared__ float red[32];
+    const int i = blockIdx.x;
+    const float* x = x32 + (size_t)rows[i] * W;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) ss = fmaf(x[c], x[c], ss);
+    ss = block_sum(ss, red);
+    const float rn = 1.f / sqrtf(ss / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) stf(out + (size_t)i * W + c, x[c] * rn * w[c]);
+}
+
+__global__ void softcap_kernel(float* __restrict__ x, int64_t n, float cap, float inv_cap) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
+inline int done() { return cudaGetLastError() == cudaSuccess ? 0 : -100; }
+
+}  // namespace
+
+int embed_sinusoid(int dt, const int64_t* ids, const int* seq_len, const void* table, int64_t vocab, float scale,
+                   const float* inv_freq, float* x32, void* xa, int S, int W, SeqPos pos, cudaStream_t s) {
+    if (!ids || !table || !inv_freq || !x32 || !xa || S < 1 || W < 2 || (W & 1)) return -2;
+    count_launch();
+    if (dt == DT_F32)
+        embed_sinusoid_kernel<float><<<S, 256, 0, s>>>(ids, seq_len, (const float*)table, vocab, scale, inv_freq, x32, (float*)xa, S, W, pos);
+    else
+        embed_sinusoid_kernel<bf16><<<S, 256, 0, s>>>(ids, seq_len, (const bf16*)table, vocab, scale, inv_freq, x32, (bf16*)xa, S, W, pos);
+    return done();
+}
+
+int postnorm_residual(int dt, float* x32, void* xa, const void* a, int ld_a, const float* wa, const void* b, int ld_b,
+                      const float* wb, const float* w, float alpha, float eps, int S, int W, cudaStream_t s) {
+    if (!x32 || !xa || !a || !w || S < 1 || W < 1 || (b && (!wa || !wb))) return -2;
+    count_launch();
+    if (dt == DT_F32)
+        postnorm_residual_kernel<float><<<S, 256, 0, s>>>(x32, (float*)xa, (const float*)a, ld_a, wa, (const float*)b, ld_b, wb, w, alpha, eps, W);
+    else
+        postnorm_residual_kernel<bf16><<<S, 256, 0, s>>>(x32, (bf16*)xa, (const bf16*)a, ld_a, wa, (const bf16*)b, ld_b, wb, w, alpha, eps, W);
+    return done();
+}
+
+int gated_group_norm(int dt, const float* y, int ld_y, const void* gate, int ld_gate, const float* w, int w_len,
+                     void* out, int ld_out, int S, int n, int group, int gate_first, float eps, cudaStream_t s) {
+    if (!y || !gate || !w || !out || S < 1 || n < 1 || group < 1 || n % group || w_len < 1) return -2;
+    const int warps = S * (n / group);
+    count_launch();
+    if (dt == DT_F32)
+        gated_group_norm_kernel<float><<<(warps + 7) / 8, 256, 0, s>>>(y, ld_y, (const float*)gate, ld_gate, w, w_len, (float*)out, ld_out, S, n, group, gate_first, eps);
+    else
+        gated_group_norm_kernel<bf16><<<(warps + 7) / 8, 256, 0, s>>>(y, ld_y, (const bf16*)gate, ld_gate, w, w_len, (bf16*)out, ld_out, S, n, group, gate_first, eps);
+    return done();
+}
+
+int glu_gelu_tanh(int dt, const void* gu, int ld, void* out, int ld_out, int S, int F, cudaStream_t s) {
+    if (!gu || !out || S < 1 || F < 1) return -2;
+    const int64_t n = (int64_t)S * F;
+    count_launch();
+    if (dt == DT_F32)
+        glu_gelu_tanh_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const float*)gu, ld, (float*)out, ld_out, S, F);
+    else
+        glu_gelu_tanh_kernel<bf16><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const bf16*)gu, ld, (bf16*)out, ld_out, S, F);
+    return done();
+}
+
+int gather_rmsnorm(int dt, const float* x32, const int* rows, const float* w, float eps, void* out, int n_rows, int W,
+                   cudaStream_t s) {
+    if (!x32 || !rows || !w || !out || n_rows < 1 || W < 1) return -2;
+    count_launch();
+    if (dt == DT_F32)
+        gather_rmsnorm_kernel<float><<<n_rows, 256, 0, s>>>(x32, rows, w, eps, (float*)out, W);
+    else
+        gather_rmsnorm_kernel<bf16><<<n_rows, 256, 0, s>>>(x32, rows, w, eps, (bf16*)out, W);
+    return done();
+}
+
+int softcap(float* x, int64_t n, float cap, cudaStream_t s) {
+    if (!x || n < 1) return -2;
+    if (!(cap > 0.f)) return 0;
+    count_launch();
+    softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(x, n, cap, 1.f / cap);
+    return done();
+}
+
+}  // namespace lcc

@@ -125,6 +125,7 @@ __device__ __forceinline__ void sample_greedy_body(const SampleArgs& a) {
         }
         if (tok == a.eos_token_id || tok == a.eos_token_id2 || n >= a.max_new_tokens) sc[LCC_SC_FINISHED] = 1;
     }
+    if (!a.embed || !a.h) return;  // models whose step embeds the token itself (it reads the id from the sequence buffer)
     const bf16* src = a.embed + (size_t)tok * a.H;
     for (int c = tid * 8; c < a.H; c += blockDim.x * 8)
         *reinterpret_cast<uint4*>(a.h + c) = *reinterpret_cast<const uint4*>(src + c);
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(1024) sample_greedy_batch_kernel(const SampleA
 }
 
 int sample_greedy(const SampleArgs& a, cudaStream_t s) {
-    if (a.V <= 0 || a.H % 8) return -1;
+    if (a.V <= 0 || (a.embed && a.H % 8)) return -1;
     lcc::count_launch();
     sample_greedy_kernel<<<1, 1024, 0, s>>>(a);
     return 0;

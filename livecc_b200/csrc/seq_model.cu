@@ -1,0 +1,330 @@
+// Native runtime of the hybrid sequence models: one C call runs a whole step (a prompt portion of any length, or one
+// decode token per sequence) over every layer and produces the logits of the wanted rows. Prefill and decode use the
+// same launch sequence; what differs is the row count and which linear kernel the shape selects.
+// The host (Python) owns every buffer; this file only sequences kernel launches.
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <vector>
+
+#include "../../include/livecc_b200.h"
+#include "cabi_common.h"
+#include "gemm.h"
+#include "launch.h"
+#include "seqmix.h"
+
+struct lcc_seq_model {
+    lcc_ctx* ctx;
+    lcc_seq_model_desc d;
+    std::vector<lcc_seq_layer> layers;
+    uint8_t* ws = nullptr;
+    size_t ws_bytes = 0;
+    int cap_tokens = 0, cap_want = 0;
+    bool use_tc = true;  // bf16 linear layers with >= 64 rows and 8-aligned shapes go to the tcgen05 GEMM (LIVECC_B200_SEQ_TC=0: never)
+};
+
+namespace {
+
+inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+
+struct Dims {
+    int inner, conv_ch, s_proj;          // SSD
+    int l_nq, l_nk, l_nv, l_proj, l_o;   // left
+    int r_nk, r_nv, r_proj;              // right
+};
+Dims dims_of(const lcc_seq_layer& L) {
+    Dims z{};
+    if (L.type == LCC_MIX_SSD) {
+        z.inner = L.s_heads * L.s_vdim;
+        z.conv_ch = z.inner + 2 * L.s_groups * L.s_state;
+        z.s_proj = z.inner + z.conv_ch + L.s_heads;
+    } else if (L.type == LCC_MIX_PARALLEL) {
+        z.l_nq = L.l_heads * L.l_dim; z.l_nk = L.l_kv_heads * L.l_dim; z.l_nv = L.l_kv_heads * L.l_vdim;
+        z.l_proj = z.l_nq + z.l_nk + z.l_nv + L.l_heads;
+        z.l_o = L.l_heads * L.l_vdim;
+        z.r_nk = L.r_heads * L.r_dim; z.r_nv = L.r_heads * L.r_vdim;
+        z.r_proj = 2 * z.r_nk + 2 * z.r_nv + L.r_rank;
+    }
+    return z;
+}
+
+// Row strides of activation buffers are rounded up to 8 elements so that every buffer a tensor-core GEMM may read or
+// write has 16-byte aligned rows.
+inline int ld8(int n) { return (n + 7) / 8 * 8; }
+
+struct WsLayout {
+    size_t x32, xa, proj, proj2, mid, mid2, y32, q32, f1, f2, o1, o2, xf, total;
+    int w_proj, w_proj2, w_mid, w_y, w_q, w_f;
+};
+
+WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
+    WsLayout L{};
+    const size_t es = lcc::dt_size(m->d.dtype);
+    const size_t nt = NT > 0 ? NT : 1, nw = NW > 0 ? NW : 1;
+    int wp = 8, wp2 = 8, wm = 8, wy = 8, wq = 8, wf = 8;
+    for (const lcc_seq_layer& l : m->layers) {
+        const Dims z = dims_of(l);
+        if (l.type == LCC_MIX_SSD) {
+            wp = std::max(wp, ld8(z.s_proj)); wm = std::max(wm, ld8(std::max(z.conv_ch, z.inner)));
+            wy = std::max(wy, z.inner); wf = std::max(wf, l.s_heads);
+        } else {
+            wp = std::max(wp, ld8(std::max(z.l_proj, z.r_proj))); wp2 = std::max(wp2, ld8(z.r_nk));
+            wm = std::max(wm, ld8(std::max(z.l_o, z.r_nv)));
+            wy = std::max(wy, z.r_nv); wq = std::max(wq, z.l_nq); wf = std::max(wf, z.r_nk);
+        }
+        if (l.ff > 0) { wp = std::max(wp, ld8(2 * l.ff)); wm = std::max(wm, ld8(l.ff)); }
+    }
+    L.w_proj = wp; L.w_proj2 = wp2; L.w_mid = wm; L.w_y = wy; L.w_q = wq; L.w_f = wf;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes); return o; };
+    const int W = m->d.width;
+    L.x32 = take(nt * W * 4);
+    L.xa = take(nt * ld8(W) * es);
+    L.proj = take(nt * wp * es);
+    L.proj2 = take(nt * wp2 * es);
+    L.mid = take(nt * wm * es);
+    L.mid2 = take(nt * wm * es);
+    L.y32 = take(nt * wy * 4);
+    L.q32 = take(nt * wq * 4);
+    L.f1 = take(nt * wf * 4);
+    L.f2 = take(nt * wf * 4);
+    L.o1 = take(nt * ld8(W) * es);
+    L.o2 = take(nt * ld8(W) * es);
+    L.xf = take(nw * ld8(W) * es);
+    L.total = off;
+    return L;
+}
+
+#define STEP(expr, what)                                                                      \
+    do {                                                                                      \
+        int rc__ = (expr);                                                                    \
+        if (rc__) LCC_FAIL(m->ctx, rc__, "%s failed (code %d)", what, rc__);                  \
+    } while (0)
+
+// y[M, N] = x[M, K] W^T (+ bias). Large bf16 products with 8-aligned shapes run on the tensor cores; everything else on
+// the CUDA-core kernels. bias_f32 is fp32; the tensor-core epilogue takes a bf16 bias (bias_bf16, may be null).
+int linear(const lcc_seq_model* m, const void* x, int ldx, const void* W, const float* bias, void* y, int ldy,
+           bool y_f32, int M, int N, int K, cudaStream_t s) {
+    if (m->use_tc && m->d.dtype == LCC_DT_BF16 && !y_f32 && !bias && M >= 64 && N >= 64 && K >= 64 && (K % 8) == 0 && (N % 8) == 0 &&
+        (ldx % 8) == 0 && (ldy % 8) == 0) {
+        lcc::GemmArgs a;
+        a.A = x; a.B = W; a.C = y; a.M = M; a.N = N; a.K = K; a.lda = ldx; a.ldb = K; a.ldc = ldy;
+        a.bias = nullptr; a.residual = nullptr; a.ldr = 0; a.epi = lcc::EPI_NONE; a.block_n = 0;
+        return lcc::gemm_bf16_tn(a, m->ctx->num_sms, s);
+    }
+    return lcc::linear_any(m->d.dtype, x, ldx, W, K, bias, y, ldy, y_f32, M, N, K, s);
+}
+
+}  // namespace
+
+extern "C" {
+
+lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc) {
+    if (!ctx || !desc || !desc->layers) return nullptr;
+    auto fail = [&](const char* msg) -> lcc_seq_model* { snprintf(ctx->err, sizeof(ctx->err), "lcc_seq_model_create: %s", msg); return nullptr; };
+    if (desc->width < 2 || (desc->width & 1) || desc->vocab < 1 || desc->n_layers < 1) return fail("bad sizes");
+    if (desc->dtype != LCC_DT_BF16 && desc->dtype != LCC_DT_F32) return fail("unknown storage type");
+    if (!desc->embed || !desc->inv_freq_f32 || !desc->final_norm_f32 || !desc->head) return fail("missing weights");
+    for (int i = 0; i < desc->n_layers; ++i) {
+        const lcc_seq_layer& l = desc->layers[i];
+        if (!l.norm1_f32 || (l.ff > 0 && (!l.norm2_f32 || !l.ff_in || !l.ff_out))) return fail("missing norm / feed-forward weights");
+        if (l.type == LCC_MIX_SSD) {
+            if (l.s_heads < 1 || l.s_vdim < 1 || l.s_state < 1 || l.s_state > 512 || l.s_groups < 1 || l.s_heads % l.s_groups ||
+                l.s_conv < 1 || l.s_conv > 8 || l.s_norm_groups < 1 || (l.s_heads * l.s_vdim) % l.s_norm_groups)
+                return fail("state-space layer: unsupported sizes");
+            if (!l.s_in || !l.s_conv_w_f32 || !l.s_conv_b_f32 || !l.s_dt_bias_f32 || !l.s_a_log_f32 || !l.s_skip_f32 || !l.s_norm_f32 || !l.s_out)
+                return fail("state-space layer: missing weights");
+        } else if (l.type == LCC_MIX_PARALLEL) {
+            if (l.l_heads < 1 || l.l_kv_heads < 1 || l.l_heads % l.l_kv_heads || l.l_dim < 1 || l.l_vdim < 1 || l.r_heads < 1 ||
+                l.r_dim < 1 || l.r_dim > 512 || l.r_vdim < 1 || l.r_rank < 1 || !(l.r_tau > 0.f))
+                return fail("parallel layer: unsupported sizes");
+            if (!l.l_in || !l.l_in_bias_f32 || !l.l_qnorm_f32 || !l.l_knorm_f32 || !l.l_out || !l.l_branch_norm_f32 || !l.r_in ||
+                !l.r_decay_up || !l.r_decay_bias_f32 || !l.r_norm_f32 || !l.r_out || !l.r_branch_norm_f32)
+                return fail("parallel layer: missing weights");
+        } else {
+            return fail("unknown mixer type");
+        }
+    }
+    lcc_seq_model* m = new lcc_seq_model();
+    m->ctx = ctx;
+    m->d = *desc;
+    m->layers.assign(desc->layers, desc->layers + desc->n_layers);
+    m->d.layers = m->layers.data();
+    const char* e = getenv("LIVECC_B200_SEQ_TC");
+    m->use_tc = !(e && e[0] == '0');
+    return m;
+}
+
+void lcc_seq_model_destroy(lcc_seq_model* m) { delete m; }
+
+size_t lcc_seq_workspace_bytes(const lcc_seq_model* m, int max_tokens, int max_want) {
+    return m ? make_layout(m, max_tokens, max_want).total : 0;
+}
+
+int lcc_seq_bind_workspace(lcc_seq_model* m, void* ws, size_t ws_bytes, int max_tokens, int max_want) {
+    if (!m || !ws) return -1;
+    if (ws_bytes < make_layout(m, max_tokens, max_want).total) LCC_FAIL(m->ctx, -2, "lcc_seq_bind_workspace: buffer too small");
+    m->ws = (uint8_t*)ws; m->ws_bytes = ws_bytes; m->cap_tokens = max_tokens; m->cap_want = max_want;
+    return 0;
+}
+
+int64_t lcc_seq_layer_state_floats(const lcc_seq_model* m, int layer) {
+    if (!m || layer < 0 || layer >= (int)m->layers.size()) return -1;
+    const lcc_seq_layer& l = m->layers[layer];
+    const Dims z = dims_of(l);
+    if (l.type == LCC_MIX_SSD) return (int64_t)z.conv_ch * (l.s_conv - 1) + (int64_t)l.s_heads * l.s_vdim * l.s_state;
+    return (int64_t)l.r_heads * l.r_vdim * l.r_dim;
+}
+
+int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entries, int page_size, const int32_t* want_rows,
+                    int n_want, float* logits, float* logits_copy, float* layer_dump, lcc_stream_t stream) {
+    if (!m || !entries || n_entries < 1) return -1;
+    if (!m->ws) LCC_FAIL(m->ctx, -3, "lcc_seq_forward: no workspace bound");
+    int T = 0;
+    for (int e = 0; e < n_entries; ++e) {
+        if (entries[e].n_new < 1 || !entries[e].ids || !entries[e].layer_state) LCC_FAIL(m->ctx, -2, "lcc_seq_forward: bad entry %d", e);
+        T += entries[e].n_new;
+    }
+    if (T > m->cap_tokens || n_want > m->cap_want) LCC_FAIL(m->ctx, -4, "lcc_seq_forward: %d rows / %d wanted exceed the bound workspace (%d / %d)", T, n_want, m->cap_tokens, m->cap_want);
+    if (n_want > 0 && (!want_rows || !logits)) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    const lcc_seq_model_desc& d = m->d;
+    const int dt = d.dtype, W = d.width;
+    const size_t es = lcc::dt_size(dt);
+    const WsLayout L = make_layout(m, m->cap_tokens, m->cap_want);
+    uint8_t* ws = m->ws;
+    float* x32 = (float*)(ws + L.x32);
+    uint8_t* xa = ws + L.xa;
+    uint8_t* proj = ws + L.proj; uint8_t* proj2 = ws + L.proj2; uint8_t* mid = ws + L.mid; uint8_t* mid2 = ws + L.mid2;
+    float* y32 = (float*)(ws + L.y32); float* q32 = (float*)(ws + L.q32);
+    float* f1 = (float*)(ws + L.f1); float* f2 = (float*)(ws + L.f2);
+    uint8_t* o1 = ws + L.o1; uint8_t* o2 = ws + L.o2; uint8_t* xf = ws + L.xf;
+    auto pos_of = [&](const lcc_seq_entry& e) {
+        lcc::SeqPos p{e.past, nullptr, nullptr};
+        if (e.scalars) { p.kv_len = e.scalars + LCC_SC_KV_LEN; p.finished = e.scalars + LCC_SC_FINISHED; }
+        return p;
+    };
+    // ---- embedding + positions ----
+    {
+        int r0 = 0;
+        for (int e = 0; e < n_entries; ++e) {
+            const lcc_seq_entry& en = entries[e];
+            STEP(lcc::embed_sinusoid(dt, en.ids, en.scalars ? en.scalars + LCC_SC_SEQ_LEN : nullptr, d.embed, d.vocab, d.embed_scale,
+                                     d.inv_freq_f32, x32 + (size_t)r0 * W, xa + (size_t)r0 * W * es, en.n_new, W, pos_of(en), s), "embedding");
+            r0 += en.n_new;
+        }
+    }
+    for (int li = 0; li < d.n_layers; ++li) {
+        const lcc_seq_layer& l = m->layers[li];
+        const Dims z = dims_of(l);
+        if (l.type == LCC_MIX_SSD) {
+            const int ldp = ld8(z.s_proj), ldm = ld8(z.conv_ch), GN = l.s_groups * l.s_state;
+            STEP(linear(m, xa, W, l.s_in, nullptr, proj, ldp, false, T, z.s_proj, W, s), "state-space in-proj");
+            STEP(lcc::ssm_step_decay(dt, proj + (size_t)(z.inner + z.conv_ch) * es, ldp, l.s_dt_bias_f32, l.s_a_log_f32, f1, f2, T,
+                                     l.s_heads, s), "step sizes");
+            int r0 = 0;
+            for (int e = 0; e < n_entries; ++e) {
+                const lcc_seq_entry& en = entries[e];
+                float* st = en.layer_state[li];
+                if (!st) LCC_FAIL(m->ctx, -2, "lcc_seq_forward: entry %d has no state for layer %d", e, li);
+                const lcc::SeqPos pos = pos_of(en);
+                uint8_t* pr = proj + (size_t)r0 * ldp * es;
+                uint8_t* xbc = mid + (size_t)r0 * ldm * es;
+                STEP(lcc::causal_conv_silu(dt, pr + (size_t)z.inner * es, ldp, xbc, ldm, l.s_conv_w_f32, l.s_conv_b_f32, st, en.n_new,
+                                           z.conv_ch, l.s_conv, pos, s), "causal convolution");
+                lcc::ScanArgs a{};
+                a.dt = dt;
+                a.k = xbc + (size_t)z.inner * es; a.ld_k = ldm;
+                a.c = xbc + (size_t)(z.inner + GN) * es; a.ld_c = ldm;
+                a.u = xbc; a.ld_u = ldm;
+                a.a = f2 + (size_t)r0 * l.s_heads; a.vec_decay = 0;
+                a.sc = f1 + (size_t)r0 * l.s_heads;
+                a.skip = l.s_skip_f32; a.cs = 1.f;
+                a.state = st + (size_t)z.conv_ch * (l.s_conv - 1);
+                a.y = y32 + (size_t)r0 * z.inner; a.ld_y = z.inner;
+                a.S = en.n_new; a.heads = l.s_heads; a.heads_per_group = l.s_heads / l.s_groups; a.N = l.s_state; a.P = l.s_vdim;
+                STEP(lcc::gated_scan(a, pos, s), "state-space recurrence");
+                r0 += en.n_new;
+            }
+            const int ldi = ld8(z.inner);
+            STEP(lcc::gated_group_norm(dt, y32, z.inner, proj, ldp, l.s_norm_f32, z.inner, mid2, ldi, T, z.inner,
+                                       z.inner / l.s_norm_groups, 1, d.eps, s), "gated norm");
+            STEP(linear(m, mid2, ldi, l.s_out, nullptr, o1, W, false, T, W, z.inner, s), "state-space out-proj");
+            STEP(lcc::postnorm_residual(dt, x32, xa, o1, W, nullptr, nullptr, 0, nullptr, l.norm1_f32, d.alpha, d.eps, T, W, s), "norm1");
+        } else {
+            // left: chunk-local attention with a sink
+            const int ldl = ld8(z.l_proj), ldo = ld8(z.l_o);
+            STEP(linear(m, xa, W, l.l_in, l.l_in_bias_f32, proj, ldl, false, T, z.l_proj, W, s), "attention in-proj");
+            int r0 = 0;
+            for (int e = 0; e < n_entries; ++e) {
+                const lcc_seq_entry& en = entries[e];
+                if (!en.k_pages || !en.v_pages || !en.k_pages[li] || !en.v_pages[li] || !en.page_table)
+                    LCC_FAIL(m->ctx, -2, "lcc_seq_forward: entry %d has no pages for layer %d", e, li);
+                const lcc::SeqPos pos = pos_of(en);
+                uint8_t* pr = proj + (size_t)r0 * ldl * es;
+                float* q = q32 + (size_t)r0 * z.l_nq;
+                STEP(lcc::qk_norm_kv_append(dt, pr, ldl, l.l_qnorm_f32, l.l_knorm_f32, d.eps, q, en.k_pages[li], en.v_pages[li],
+                                            en.page_table, page_size, en.n_new, l.l_heads, l.l_kv_heads, l.l_dim, l.l_vdim, pos, s),
+                     "q/k norm + cache append");
+                STEP(lcc::attn_chunk_sink(dt, q, en.k_pages[li], en.v_pages[li], en.page_table, page_size,
+                                          pr + (size_t)(z.l_nq + z.l_nk + z.l_nv) * es, ldl, mid + (size_t)r0 * ldo * es, ldo, en.n_new,
+                                          l.l_heads, l.l_kv_heads, l.l_dim, l.l_vdim, l.l_chunk, l.l_scale, pos, s), "chunk attention");
+                r0 += en.n_new;
+            }
+            STEP(linear(m, mid, ldo, l.l_out, nullptr, o1, W, false, T, W, z.l_o, s), "attention out-proj");
+            // right: gated linear attention
+            const int ldr = ld8(z.r_proj), ldz = ld8(z.r_nk), ldv = ld8(z.r_nv);
+            STEP(linear(m, xa, W, l.r_in, nullptr, proj, ldr, false, T, z.r_proj, W, s), "linear-attention in-proj");
+            STEP(linear(m, proj + (size_t)(2 * z.r_nk + 2 * z.r_nv) * es, ldr, l.r_decay_up, l.r_decay_bias_f32, proj2, ldz, false, T, z.r_nk, l.r_rank, s), "decay projection");
+            STEP(lcc::gla_decay(dt, proj2, ldz, nullptr, l.r_tau, f1, T, z.r_nk, s), "decays");
+            r0 = 0;
+            for (int e = 0; e < n_entries; ++e) {
+                const lcc_seq_entry& en = entries[e];
+                float* st = en.layer_state[li];
+                if (!st) LCC_FAIL(m->ctx, -2, "lcc_seq_forward: entry %d has no state for layer %d", e, li);
+                uint8_t* pr = proj + (size_t)r0 * ldr * es;
+                lcc::ScanArgs a{};
+                a.dt = dt;
+                a.k = pr + (size_t)z.r_nk * es; a.ld_k = ldr;
+                a.c = pr; a.ld_c = ldr;
+                a.u = pr + (size_t)(2 * z.r_nk) * es; a.ld_u = ldr;
+                a.a = f1 + (size_t)r0 * z.r_nk; a.vec_decay = 1;
+                a.sc = nullptr; a.skip = nullptr; a.cs = 1.f / sqrtf((float)l.r_dim);
+                a.state = st;
+                a.y = y32 + (size_t)r0 * z.r_nv; a.ld_y = z.r_nv;
+                a.S = en.n_new; a.heads = l.r_heads; a.heads_per_group = 1; a.N = l.r_dim; a.P = l.r_vdim;
+                STEP(lcc::gated_scan(a, pos_of(en), s), "linear-attention recurrence");
+                r0 += en.n_new;
+            }
+            STEP(lcc::gated_group_norm(dt, y32, z.r_nv, proj + (size_t)(2 * z.r_nk + z.r_nv) * es, ldr, l.r_norm_f32, l.r_vdim, mid2, ldv, T,
+                                       z.r_nv, l.r_vdim, 0, d.eps, s), "head norm + gate");
+            STEP(linear(m, mid2, ldv, l.r_out, nullptr, o2, W, false, T, W, z.r_nv, s), "linear-attention out-proj");
+            STEP(lcc::postnorm_residual(dt, x32, xa, o1, W, l.l_branch_norm_f32, o2, W, l.r_branch_norm_f32, l.norm1_f32, d.alpha, d.eps,
+                                        T, W, s), "branch merge + norm1");
+        }
+        if (l.ff > 0) {
+            const int ldg = ld8(2 * l.ff), ldf = ld8(l.ff);
+            STEP(linear(m, xa, W, l.ff_in, nullptr, proj, ldg, false, T, 2 * l.ff, W, s), "feed-forward in");
+            STEP(lcc::glu_gelu_tanh(dt, proj, ldg, mid, ldf, T, l.ff, s), "gated gelu");
+            STEP(linear(m, mid, ldf, l.ff_out, nullptr, o1, W, false, T, W, l.ff, s), "feed-forward out");
+            STEP(lcc::postnorm_residual(dt, x32, xa, o1, W, nullptr, nullptr, 0, nullptr, l.norm2_f32, d.alpha, d.eps, T, W, s), "norm2");
+        }
+        if (layer_dump) {
+            if (cudaMemcpyAsync(layer_dump + (size_t)li * T * W, x32, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+                LCC_FAIL(m->ctx, -100, "layer dump copy failed");
+        }
+    }
+    if (n_want > 0) {
+        STEP(lcc::gather_rmsnorm(dt, x32, want_rows, d.final_norm_f32, d.eps, xf, n_want, W, s), "final norm");
+        STEP(lcc::linear_any(dt, xf, W, d.head, W, nullptr, logits, d.vocab, true, n_want, d.vocab, W, s), "output head");
+        STEP(lcc::softcap(logits, (int64_t)n_want * d.vocab, d.logit_softcap, s), "logit soft cap");
+        if (logits_copy &&
+            cudaMemcpyAsync(logits_copy, logits, (size_t)n_want * d.vocab * 4, cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+            LCC_FAIL(m->ctx, -100, "logits copy failed");
+    }
+    LCC_CHECK_LAUNCH(m->ctx, "lcc_seq_forward");
+    return 0;
+}
+
+}  // extern "C"

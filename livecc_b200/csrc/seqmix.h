@@ -1,0 +1,106 @@
+// Internal launch interfaces of the sequence-mixing ops used by the hybrid decoder models (state-space layers, gated
+// linear attention, chunk-local attention with a softmax sink, post-norm residual blocks):
+//   linear_any.cu   general-shape linear layers (any M, N, K; bf16 or fp32 storage, fp32 accumulation)
+//   recurrent.cu    short causal convolution with carried inputs, gated linear recurrences with carried fp32 state
+//   attn_local.cu   whole-projection q/k norm + paged K/V append, chunk-local attention with a sink term
+//   rowops.cu       embedding + sinusoidal positions, post-norm residual, grouped gated RMS norm, GLU, soft cap
+// Every op exists for two storage types (DT_BF16: bf16 storage, fp32 arithmetic where the model asks for it;
+// DT_F32: everything fp32). All return 0 on success, negative on invalid arguments; launches are asynchronous on `s`.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace lcc {
+
+enum { DT_BF16 = 0, DT_F32 = 1 };
+inline size_t dt_size(int dt) { return dt == DT_F32 ? 4 : 2; }
+
+// A sequence position source: `past` tokens precede row 0 of this call. When `kv_len` is non-null the kernels read
+// past = *kv_len from the device instead (CUDA-graph replay of decode steps), and do nothing when `*finished` is set.
+struct SeqPos {
+    int past;
+    const int* kv_len;
+    const int* finished;
+};
+
+// ---- linear_any.cu ------------------------------------------------------------------------------------------------------
+// C[M,N] = A[M,K] x W[N,K]^T (+ bias[N], fp32). A and W have storage type dt; C has storage type dt, or fp32 when
+// c_f32. Any M, N, K >= 1; leading dimensions in elements.
+int linear_any(int dt, const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, bool c_f32,
+               int M, int N, int K, cudaStream_t s);
+
+// ---- recurrent.cu -------------------------------------------------------------------------------------------------------
+// Causal per-channel convolution over `taps` inputs followed by silu. in/out: [S, C] slices (storage dt, leading
+// dimensions ld_in / ld_out); w: fp32 [C, taps] (last column multiplies the current token); b: fp32 [C];
+// carry: fp32 [C, taps-1] = the last taps-1 inputs before row 0 (zeros at the start of a sequence), updated to the last
+// taps-1 inputs of this call.
+int causal_conv_silu(int dt, const void* in, int ld_in, void* out, int ld_out, const float* w, const float* b,
+                     float* carry, int S, int C, int taps, SeqPos pos, cudaStream_t s);
+
+// Step sizes and decays of a scalar-decay state-space layer: dt = softplus(raw + dt_bias[h]), decay = exp(-exp(a_log[h]) * dt).
+// raw: [S, heads] slice (storage dt, leading dimension ld); dt_out / decay_out: fp32 [S, heads].
+int ssm_step_decay(int dt, const void* raw, int ld, const float* dt_bias, const float* a_log, float* dt_out,
+                   float* decay_out, int S, int heads, cudaStream_t s);
+// Per-channel decays of gated linear attention: decay = sigmoid(z + bias)^(1/tau); z: [S, n] slice (storage dt).
+int gla_decay(int dt, const void* z, int ld, const float* bias, float tau, float* decay_out, int S, int n,
+              cudaStream_t s);
+
+// Gated linear recurrence, one state matrix St[n, p] (n < N key channels, p < P value channels) per head:
+//     St <- diag(a_t) St + k_t (sc_t * u_t)^T ,   y_t = St^T (cs * c_t) + skip[h] * u_t
+// k, c: [S, *] slices with head-group stride (head h reads columns (h / heads_per_group) * N + n); u: [S, heads*P] slice;
+// a: fp32, either [S, heads] (vec_decay = 0) or [S, heads*N]; sc: fp32 [S, heads] or null (= 1); skip: fp32 [heads] or null.
+// state: fp32 [heads, P, N] (n fastest), read at the start and written back at the end. y: fp32 [S, heads*P].
+struct ScanArgs {
+    int dt;
+    const void* k; int ld_k;
+    const void* c; int ld_c;
+    const void* u; int ld_u;
+    const float* a; int vec_decay;
+    const float* sc;
+    const float* skip;
+    float cs;
+    float* state;
+    float* y; int ld_y;
+    int S, heads, heads_per_group, N, P;
+};
+int gated_scan(const ScanArgs& a, SeqPos pos, cudaStream_t s);
+
+// ---- attn_local.cu ------------------------------------------------------------------------------------------------------
+// RMS norm of the whole q projection and of the whole k projection of each row (weights qn_w [Hq*D], kn_w [G*D], fp32),
+// then: normalised q -> q_out fp32 [S, Hq*D]; normalised k and raw v -> the paged cache at positions past..past+S-1.
+// proj: [S, ld] rows laid out [q: Hq*D | k: G*D | v: G*DV | ...] (storage dt). K pages: [page][G][page_size][D],
+// V pages: [page][G][page_size][DV] (storage dt).
+int qk_norm_kv_append(int dt, const void* proj, int ld, const float* qn_w, const float* kn_w, float eps, float* q_out,
+                      void* k_pages, void* v_pages, const int* page_table, int page_size, int S, int Hq, int G, int D,
+                      int DV, SeqPos pos, cudaStream_t s);
+// Attention of S new rows over the cached keys of the same chunk: row at position i sees j <= i with
+// floor(j / chunk) == floor(i / chunk); weights exp(s_j) / (1 + sum_j exp(s_j)) (a sink with score 0 and no value);
+// head h's output is multiplied by sigmoid(gate[h]). q: fp32 [S, Hq*D]; gate: [S, Hq] slice (storage dt, leading dim
+// ld_gate) or null; out: [S, Hq*DV] (storage dt). chunk <= 0 means one chunk (plain causal attention).
+int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_pages, const int* page_table,
+                    int page_size, const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D,
+                    int DV, int chunk, float scale, SeqPos pos, cudaStream_t s);
+
+// ---- rowops.cu ----------------------------------------------------------------------------------------------------------
+// x[r, :] = table[id_r, :] * scale + sinusoid(past + r): entry 2i = sin(p * inv_freq[i]), 2i+1 = cos of the same.
+// ids: device int64; when seq_len is non-null, row r reads ids[*seq_len - S + r]. x32: fp32 [S, W]; xa: copy in storage dt.
+int embed_sinusoid(int dt, const int64_t* ids, const int* seq_len, const void* table, int64_t vocab, float scale,
+                   const float* inv_freq, float* x32, void* xa, int S, int W, SeqPos pos, cudaStream_t s);
+// Post-norm residual block: m = a, or (two branches) m = (rms(a) * wa + rms(b) * wb) / 2; x <- rms(alpha * x + m) * w.
+// a, b: [S, W] (storage dt); wa, wb, w: fp32 [W]; x32 updated in place, xa = copy in storage dt.
+int postnorm_residual(int dt, float* x32, void* xa, const void* a, int ld_a, const float* wa, const void* b, int ld_b,
+                      const float* wb, const float* w, float alpha, float eps, int S, int W, cudaStream_t s);
+// Grouped RMS norm with a multiplicative silu gate: y: fp32 [S, n]; gate: [S, n] slice (storage dt). Groups of `group`
+// consecutive columns; weight w[c % w_len]. gate_first: out = rms(y * silu(g)) * w, else out = rms(y) * w * silu(g).
+int gated_group_norm(int dt, const float* y, int ld_y, const void* gate, int ld_gate, const float* w, int w_len,
+                     void* out, int ld_out, int S, int n, int group, int gate_first, float eps, cudaStream_t s);
+// out[r, c] = gelu_tanh(gu[r, c]) * gu[r, F + c]
+int glu_gelu_tanh(int dt, const void* gu, int ld, void* out, int ld_out, int S, int F, cudaStream_t s);
+// out[i, :] = rms(x32[rows[i], :]) * w  (storage dt)
+int gather_rmsnorm(int dt, const float* x32, const int* rows, const float* w, float eps, void* out, int n_rows, int W,
+                   cudaStream_t s);
+// x <- cap * tanh(x / cap) in place (fp32); cap <= 0: unchanged
+int softcap(float* x, int64_t n, float cap, cudaStream_t s);
+
+}  // namespace lcc

@@ -18,32 +18,25 @@ import torch
 from ._cabi import PAGE_SIZE, SC_COUNT, StreamState
 
 
-class PagePool:
-    """Fixed-size pages shared by all streams of one engine. Grows by doubling (rare)."""
+class PageAllocator:
+    """Free list of fixed-size pages; storage is the subclass's (`_resize_storage` re-creates it for a new page count and
+    copies the old pages over). Grows by doubling (rare)."""
 
-    def __init__(self, layers: int, kv_heads: int, device, initial_pages: int = 160):
-        self.layers, self.kv_heads, self.device = layers, kv_heads, device
+    def __init__(self, device, initial_pages: int):
+        self.device = device
         self.num_pages = 0
-        self.k = self.v = None
         self.free: List[int] = []
         self.generation = 0  # bumped whenever the pool storage moves (invalidates captured graphs)
-        self._free_buffers: List["StreamBuffers"] = []
         self._grow(initial_pages)
 
-    def _grow(self, new_total: int):
-        shape = (self.layers, new_total, self.kv_heads, PAGE_SIZE, 128)
-        k = torch.empty(shape, dtype=torch.bfloat16, device=self.device)
-        v = torch.empty(shape, dtype=torch.bfloat16, device=self.device)
-        if self.k is not None:
-            k[:, : self.num_pages].copy_(self.k)
-            v[:, : self.num_pages].copy_(self.v)
-        self.free.extend(range(self.num_pages, new_total))
-        self.k, self.v, self.num_pages = k, v, new_total
-        self.generation += 1
+    def _resize_storage(self, new_total: int):
+        raise NotImplementedError
 
-    @property
-    def layer_stride(self) -> int:
-        return self.num_pages * self.kv_heads * PAGE_SIZE * 128
+    def _grow(self, new_total: int):
+        self._resize_storage(new_total)
+        self.free.extend(range(self.num_pages, new_total))
+        self.num_pages = new_total
+        self.generation += 1
 
     def alloc(self, n: int) -> List[int]:
         while len(self.free) < n:
@@ -54,6 +47,29 @@ class PagePool:
 
     def release(self, pages: List[int]):
         self.free.extend(pages)
+
+
+class PagePool(PageAllocator):
+    """Fixed-size pages shared by all streams of one engine (every layer has the same K/V geometry, head size 128)."""
+
+    def __init__(self, layers: int, kv_heads: int, device, initial_pages: int = 160):
+        self.layers, self.kv_heads = layers, kv_heads
+        self.k = self.v = None
+        self._free_buffers: List["StreamBuffers"] = []
+        super().__init__(device, initial_pages)
+
+    def _resize_storage(self, new_total: int):
+        shape = (self.layers, new_total, self.kv_heads, PAGE_SIZE, 128)
+        k = torch.empty(shape, dtype=torch.bfloat16, device=self.device)
+        v = torch.empty(shape, dtype=torch.bfloat16, device=self.device)
+        if self.k is not None:
+            k[:, : self.num_pages].copy_(self.k)
+            v[:, : self.num_pages].copy_(self.v)
+        self.k, self.v = k, v
+
+    @property
+    def layer_stride(self) -> int:
+        return self.num_pages * self.kv_heads * PAGE_SIZE * 128
 
     # Per-stream device buffers (page table, scalars, id buffer) are recycled through the pool so that their
     # addresses — which are baked into captured decode graphs — stay stable from one stream to the next.
@@ -166,3 +182,153 @@ class PagedKVCache:
         k = self.pool.k[layer][idx].permute(1, 0, 2, 3).reshape(self.pool.kv_heads, -1, 128)[:, : self.seq_len]
         v = self.pool.v[layer][idx].permute(1, 0, 2, 3).reshape(self.pool.kv_heads, -1, 128)[:, : self.seq_len]
         return k, v
+
+
+# ------------------------------------------------------------------------------------------------
+# Hybrid sequence models: pages for the attention layers + fp32 state slots for the recurrent layers
+# ------------------------------------------------------------------------------------------------
+class SeqStatePool(PageAllocator):
+    """Memory of every live sequence of one hybrid-model engine.
+
+    * Attention layers: K pages [num_pages, kv_heads, PAGE_SIZE, dim] and V pages [num_pages, kv_heads, PAGE_SIZE, vdim]
+      per layer (layers may differ in geometry; page ids are shared by all layers). A chunk-local layer never looks
+      behind the start of the current chunk, so a sequence gives pages back as soon as every attention layer has left them.
+    * Recurrent layers: one fp32 slot per sequence and layer (`state_floats[i]` elements, 0 for none), zeroed when a
+      sequence takes it.
+    attn_layers: {layer index: (kv_heads, dim, vdim, chunk)}; state_floats: per layer."""
+
+    def __init__(self, attn_layers: dict, state_floats: List[int], dtype, device, initial_pages: int = 32, initial_slots: int = 2):
+        self.attn_layers = dict(attn_layers)
+        self.state_floats = list(state_floats)
+        self.dtype = dtype
+        self.k = {i: None for i in self.attn_layers}
+        self.v = {i: None for i in self.attn_layers}
+        self.num_slots = 0
+        self.free_slots: List[int] = []
+        self.state: List[Optional[torch.Tensor]] = [None] * len(self.state_floats)
+        super().__init__(device, max(1, initial_pages) if self.attn_layers else 0)
+        self.device = device
+        self._grow_slots(max(1, initial_slots))
+
+    # pages ------------------------------------------------------------------------------------
+    def _resize_storage(self, new_total: int):
+        for i, (g, d, dv, _chunk) in self.attn_layers.items():
+            k = torch.zeros((new_total, g, PAGE_SIZE, d), dtype=self.dtype, device=self.device)
+            v = torch.zeros((new_total, g, PAGE_SIZE, dv), dtype=self.dtype, device=self.device)
+            if self.k[i] is not None:
+                k[: self.num_pages].copy_(self.k[i])
+                v[: self.num_pages].copy_(self.v[i])
+            self.k[i], self.v[i] = k, v
+
+    def keep_from(self, seq_len: int) -> int:
+        """First position any attention layer can still read once `seq_len` tokens are cached."""
+        if not self.attn_layers:
+            return seq_len
+        lo = seq_len
+        for (_g, _d, _dv, chunk) in self.attn_layers.values():
+            lo = min(lo, (seq_len // chunk) * chunk if chunk > 0 else 0)
+        return lo
+
+    # state slots ------------------------------------------------------------------------------
+    def _grow_slots(self, new_total: int):
+        for i, n in enumerate(self.state_floats):
+            if n <= 0:
+                continue
+            t = torch.zeros((new_total, n), dtype=torch.float32, device=self.device)
+            if self.state[i] is not None:
+                t[: self.num_slots].copy_(self.state[i])
+            self.state[i] = t
+        self.free_slots.extend(range(self.num_slots, new_total))
+        self.num_slots = new_total
+        self.generation += 1
+
+    def acquire_slot(self) -> int:
+        if not self.free_slots:
+            self._grow_slots(self.num_slots * 2)
+        slot = self.free_slots.pop(0)
+        for t in self.state:
+            if t is not None:
+                t[slot].zero_()   # a sequence starts from the zero state, whoever used the slot before
+        return slot
+
+    def release_slot(self, slot: int):
+        self.free_slots.append(slot)
+
+    def bytes_per_token(self) -> int:
+        es = torch.empty((), dtype=self.dtype).element_size()
+        return sum(g * (d + dv) * es for (g, d, dv, _c) in self.attn_layers.values())
+
+    def state_bytes_per_sequence(self) -> int:
+        return 4 * sum(self.state_floats)
+
+
+class SeqCache:
+    """One sequence of a hybrid model: its state slot, its pages, its length, and (for generation) the device scalars and
+    id buffer that the token-selection kernel advances. The HF-cache surface (`get_seq_length`) matches PagedKVCache."""
+
+    def __init__(self, pool: SeqStatePool):
+        self.pool = pool
+        self.slot: Optional[int] = pool.acquire_slot()
+        self.pages: List[Optional[int]] = []   # logical page -> physical page, None once given back
+        self.seq_len = 0
+        self.page_table = torch.zeros(64, dtype=torch.int32, device=pool.device)
+        self.scalars = torch.zeros(SC_COUNT, dtype=torch.int32, device=pool.device)
+        self.seq_buf: Optional[torch.Tensor] = None
+        self.table_generation = 0
+
+    def get_seq_length(self, layer_idx: int = 0) -> int:
+        return self.seq_len
+
+    def ensure_tokens(self, n_tokens: int):
+        """Pages for positions [keep_from(seq_len), n_tokens)."""
+        if not self.pool.attn_layers:
+            return
+        need = (n_tokens + PAGE_SIZE - 1) // PAGE_SIZE
+        first_new = len(self.pages)
+        if need > first_new:
+            self.pages.extend(self.pool.alloc(need - first_new))
+            if need > self.page_table.numel():
+                t = torch.zeros(max(need, 2 * self.page_table.numel()), dtype=torch.int32, device=self.pool.device)
+                t[: self.page_table.numel()].copy_(self.page_table)
+                self.page_table = t
+                self.table_generation += 1
+            host = torch.tensor(self.pages[first_new:need], dtype=torch.int32)
+            self.page_table[first_new:need].copy_(host)
+
+    def ensure_seq_capacity(self, n_ids: int):
+        if self.seq_buf is None or n_ids > self.seq_buf.numel():
+            t = torch.zeros(max(n_ids, 1024, 2 * (self.seq_buf.numel() if self.seq_buf is not None else 0)),
+                            dtype=torch.int64, device=self.pool.device)
+            if self.seq_buf is not None:
+                t[: self.seq_buf.numel()].copy_(self.seq_buf)
+            self.seq_buf = t
+            self.table_generation += 1
+
+    def advance(self, n_new: int):
+        """`n_new` more tokens are cached; pages every attention layer has left go back to the pool."""
+        self.seq_len += n_new
+        last_dead = self.pool.keep_from(self.seq_len) // PAGE_SIZE
+        dead = [p for p in self.pages[:last_dead] if p is not None]
+        if dead:
+            self.pool.release(dead)
+            for i in range(min(last_dead, len(self.pages))):
+                self.pages[i] = None
+
+    def live_pages(self) -> int:
+        return sum(p is not None for p in self.pages)
+
+    def release(self):
+        if self.slot is not None:
+            self.pool.release_slot(self.slot)
+            self.slot = None
+        live = [p for p in self.pages if p is not None]
+        if live:
+            self.pool.release(live)
+        self.pages = []
+        self.seq_len = 0
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass

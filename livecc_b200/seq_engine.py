@@ -1,0 +1,384 @@
+"""Hybrid sequence models (decoder-only language models built from state-space, gated-linear-attention and chunk-local
+attention mixers) behind the same surface as the video-language engine: `from_pretrained`, `generate`, a cache object that
+callers pass back, greedy token selection in the library's sampling kernel.
+
+    model = SeqLMForCausalLM.from_pretrained(path, torch_dtype="bfloat16", device_map="cuda")
+    out = model.generate(input_ids, max_new_tokens=16)            # out.sequences, out.past_key_values
+    logits = model.forward_step([(cache, ids)], [[0, 2]])         # teacher-forced step: logits of chosen rows
+
+Everything numeric runs in the native library (csrc/seq_model.cu sequences one step; linear_any.cu / gemm_tcgen05.cu,
+recurrent.cu, attn_local.cu, rowops.cu hold the kernels); this file is host orchestration: weight layout, state slots and
+pages, step bookkeeping, CUDA-graph replay of the decode step. There is no CPU or eager fallback.
+
+Two storage types: bf16 (weights, activations and K/V pages in bf16; the residual stream, norms, scores, recurrent state
+and everything entering a recurrence in fp32) and fp32 (everything fp32, plain FMAs).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _cabi
+from .config import SeqModelConfig
+from .engine import GenerateOutput
+from .kv_cache import PAGE_SIZE, SeqCache, SeqStatePool
+
+
+def _dtype_of(torch_dtype) -> torch.dtype:
+    if torch_dtype in ("auto", None, torch.bfloat16, "bfloat16", "bf16"):
+        return torch.bfloat16
+    if torch_dtype in (torch.float32, "float32", "fp32", "float"):
+        return torch.float32
+    raise NotImplementedError(f"torch_dtype={torch_dtype!r}: the hybrid sequence models run in bfloat16 or float32")
+
+
+class SeqWeights:
+    """Device tensors in the layout the library reads: fused input projections per mixer, fp32 norms / biases / per-head
+    parameters, matrices in the storage type."""
+
+    def __init__(self, cfg: SeqModelConfig, tensors, dtype: torch.dtype, device):
+        t: Dict[str, torch.Tensor] = dict(tensors)
+        self.dtype = dtype
+        used = set()
+
+        def get(name):
+            if name not in t:
+                raise KeyError(f"checkpoint has no tensor {name!r}")
+            used.add(name)
+            return t[name]
+
+        def mat(*names):   # rows of several [out, in] matrices stacked into one
+            return torch.cat([get(n).to(torch.float32) for n in names], 0).to(device=device, dtype=dtype).contiguous()
+
+        def f32(x):
+            return x.to(device=device, dtype=torch.float32).contiguous()
+
+        W = cfg.width
+        self.embed = mat("embed")
+        self.head = mat("head")
+        self.final_norm = f32(get("final.norm"))
+        if self.embed.shape != (cfg.vocab, W) or self.head.shape != (cfg.vocab, W):
+            raise ValueError("embed / head do not have the shape [vocab, width] of config.json")
+        i2 = torch.arange(0, W, 2, dtype=torch.float32)
+        self.inv_freq = torch.pow(torch.tensor(10000.0, dtype=torch.float32), -i2 / W).to(device)
+        self.layers: List[dict] = []
+        for i, L in enumerate(cfg.layers):
+            p = f"l{i}."
+            w = {"norm1": f32(get(p + "norm1"))}
+            if L.type == "mamba2":
+                s = L.ssd
+                m = p + "mix."
+                w["s_in"] = mat(m + "in")
+                if w["s_in"].shape != (s.proj_rows, W):
+                    raise ValueError(f"{m}in has shape {tuple(w['s_in'].shape)}, config.json implies {(s.proj_rows, W)}")
+                w["s_conv_w"] = f32(get(m + "conv"))
+                if w["s_conv_w"].shape != (s.conv_channels, s.conv):
+                    raise ValueError(f"{m}conv has shape {tuple(w['s_conv_w'].shape)}, expected {(s.conv_channels, s.conv)}")
+                w["s_conv_b"] = f32(get(m + "conv.b"))
+                w["s_dt_bias"] = f32(get(m + "dt_bias"))
+                w["s_a_log"] = f32(get(m + "A_log"))
+                w["s_skip"] = f32(get(m + "D"))
+                w["s_norm"] = f32(get(m + "norm"))
+                w["s_out"] = mat(m + "o")
+            else:
+                l, r = L.left, L.right
+                a, b = p + "mix.left.", p + "mix.right."
+                w["l_in"] = mat(a + "q", a + "k", a + "v", a + "g")
+                w["l_in_bias"] = f32(torch.cat([get(a + "q.b").float(), get(a + "k.b").float(), get(a + "v.b").float(),
+                                                torch.zeros(l.heads)]))
+                if w["l_in"].shape[0] != l.heads * l.dim + l.kv_heads * (l.dim + l.vdim) + l.heads:
+                    raise ValueError(f"layer {i}: left projections do not match config.json")
+                w["l_qnorm"] = f32(get(a + "q.norm"))
+                w["l_knorm"] = f32(get(a + "k.norm"))
+                w["l_out"] = mat(a + "o")
+                w["l_branch_norm"] = f32(get(a + "out"))
+                r.rank = int(get(b + "a1").shape[0])
+                w["r_in"] = mat(b + "q", b + "k", b + "v", b + "g", b + "a1")
+                if w["r_in"].shape[0] != 2 * r.heads * r.dim + 2 * r.heads * r.vdim + r.rank:
+                    raise ValueError(f"layer {i}: right projections do not match config.json")
+                w["r_decay_up"] = mat(b + "a2")
+                w["r_decay_bias"] = f32(get(b + "a2.b"))
+                w["r_norm"] = f32(get(b + "norm"))
+                w["r_out"] = mat(b + "o")
+                w["r_branch_norm"] = f32(get(b + "out"))
+            if L.ff:
+                w["norm2"] = f32(get(p + "norm2"))
+                w["ff_in"] = mat(p + "mlp.gate", p + "mlp.up")
+                w["ff_out"] = mat(p + "mlp.down")
+                if w["ff_in"].shape != (2 * L.ff, W):
+                    raise ValueError(f"layer {i}: feed-forward width does not match config.json")
+            self.layers.append(w)
+        self.unused = sorted(set(t) - used)
+
+    def nbytes(self) -> int:
+        n = sum(x.numel() * x.element_size() for x in (self.embed, self.head, self.final_norm))
+        return n + sum(x.numel() * x.element_size() for w in self.layers for x in w.values())
+
+
+class SeqLMForCausalLM:
+    PROFILE = "seq"   # the subset of native sources this family needs (livecc_b200.build.PROFILES)
+
+    def __init__(self, config: SeqModelConfig, weights: SeqWeights, device: torch.device, max_tokens: int = 0):
+        config.validate()
+        if device.type != "cuda":
+            raise _cabi.LiveCCNativeError("the hybrid sequence models need a CUDA (sm_100a) device; there is no CPU path")
+        self.config, self.weights, self.device, self.dtype = config, weights, device, weights.dtype
+        torch.cuda.set_device(device)
+        self.ctx = _cabi.Context(device.index if device.index is not None else torch.cuda.current_device(), profile=self.PROFILE)
+        self._native = self._build_native()
+        attn = {i: (L.left.kv_heads, L.left.dim, L.left.vdim, L.left.chunk) for i, L in enumerate(config.layers) if L.type == "parallel"}
+        pages = (max_tokens + PAGE_SIZE - 1) // PAGE_SIZE + 2 if max_tokens else 32
+        self.pool = SeqStatePool(attn, self._native.state_floats(), self.dtype, device, initial_pages=pages)
+        self._ensure_workspace(max(256, min(max_tokens, 4096)) if max_tokens else 1024, 64)
+        self.generation_eos = config.eos_token_id
+        self._logits_proc = torch.empty((config.vocab,), dtype=torch.float32, device=device)
+        self._graphs = {}
+        self.use_cuda_graph = os.environ.get("LIVECC_B200_NO_GRAPH", "0") != "1"
+        self.last_stats = {}
+
+    # -- construction --------------------------------------------------------------------------------------------
+    @classmethod
+    def from_state_dict(cls, config: SeqModelConfig, tensors, torch_dtype="bfloat16", device="cuda", max_tokens: int = 0):
+        device = torch.device(device if ":" in str(device) else f"{device}:{torch.cuda.current_device()}")
+        return cls(config, SeqWeights(config, tensors, _dtype_of(torch_dtype), device), device, max_tokens)
+
+    @classmethod
+    def from_pretrained(cls, model_path: str, torch_dtype="auto", device_map="cuda", max_tokens: int = 0, **_):
+        """A directory with config.json and *.safetensors (bf16 tensors; names `embed`, `l<i>.norm1`, `l<i>.mix.*`,
+        `l<i>.mlp.*`, `final.norm`, `head`)."""
+        from .checkpoint import iter_safetensors
+
+        with open(os.path.join(model_path, "config.json")) as f:
+            cfg = SeqModelConfig.from_json(json.load(f))
+        return cls.from_state_dict(cfg, iter_safetensors(model_path), torch_dtype,
+                                   device_map if isinstance(device_map, str) else "cuda", max_tokens)
+
+    def _build_native(self) -> _cabi.SeqNativeModel:
+        cfg, w = self.config, self.weights
+        p = lambda x: x.data_ptr() if x is not None else None
+        arr = (_cabi.SeqLayer * len(cfg.layers))()
+        for i, (L, lw) in enumerate(zip(cfg.layers, w.layers)):
+            e = arr[i]
+            e.ff = L.ff
+            e.norm1_f32 = p(lw["norm1"])
+            if L.type == "mamba2":
+                s = L.ssd
+                e.type = _cabi.MIX_SSD
+                e.s_heads, e.s_vdim, e.s_state, e.s_groups, e.s_conv, e.s_norm_groups = s.heads, s.vdim, s.state, s.groups, s.conv, s.norm_groups
+                e.s_in, e.s_conv_w_f32, e.s_conv_b_f32 = p(lw["s_in"]), p(lw["s_conv_w"]), p(lw["s_conv_b"])
+                e.s_dt_bias_f32, e.s_a_log_f32, e.s_skip_f32 = p(lw["s_dt_bias"]), p(lw["s_a_log"]), p(lw["s_skip"])
+                e.s_norm_f32, e.s_out = p(lw["s_norm"]), p(lw["s_out"])
+            else:
+                l, r = L.left, L.right
+                e.type = _cabi.MIX_PARALLEL
+                e.l_heads, e.l_kv_heads, e.l_dim, e.l_vdim, e.l_chunk, e.l_scale = l.heads, l.kv_heads, l.dim, l.vdim, l.chunk, l.scale
+                e.r_heads, e.r_dim, e.r_vdim, e.r_rank, e.r_tau = r.heads, r.dim, r.vdim, r.rank, r.tau
+                e.l_in, e.l_in_bias_f32, e.l_qnorm_f32, e.l_knorm_f32 = p(lw["l_in"]), p(lw["l_in_bias"]), p(lw["l_qnorm"]), p(lw["l_knorm"])
+                e.l_out, e.l_branch_norm_f32 = p(lw["l_out"]), p(lw["l_branch_norm"])
+                e.r_in, e.r_decay_up, e.r_decay_bias_f32 = p(lw["r_in"]), p(lw["r_decay_up"]), p(lw["r_decay_bias"])
+                e.r_norm_f32, e.r_out, e.r_branch_norm_f32 = p(lw["r_norm"]), p(lw["r_out"]), p(lw["r_branch_norm"])
+            if L.ff:
+                e.norm2_f32, e.ff_in, e.ff_out = p(lw["norm2"]), p(lw["ff_in"]), p(lw["ff_out"])
+        desc = _cabi.SeqModelDesc(
+            width=cfg.width, vocab=cfg.vocab, n_layers=len(cfg.layers),
+            dtype=_cabi.DT_F32 if self.dtype == torch.float32 else _cabi.DT_BF16, eps=cfg.eps, alpha=cfg.alpha,
+            embed_scale=cfg.embed_scale, logit_softcap=cfg.logit_softcap, embed=p(w.embed), inv_freq_f32=p(w.inv_freq),
+            final_norm_f32=p(w.final_norm), head=p(w.head), layers=arr)
+        return _cabi.SeqNativeModel(self.ctx, desc, keepalive=(arr, w))
+
+    def _ensure_workspace(self, tokens: int, want: int):
+        n = self._native
+        if tokens <= n.cap_tokens and want <= n.cap_want:
+            return
+        torch.cuda.synchronize(self.device)
+        n.bind_workspace(max(tokens, n.cap_tokens), max(want, n.cap_want), self.device)
+        self._graphs = {}
+
+    # -- HF-surface helpers ----------------------------------------------------------------------------------------
+    def eval(self):
+        return self
+
+    def to(self, *_, **__):
+        return self
+
+    def new_cache(self) -> SeqCache:
+        return SeqCache(self.pool)
+
+    def kernel_launches(self) -> int:
+        return _cabi.launch_count()
+
+    # -- one step ----------------------------------------------------------------------------------------------------
+    def _entry(self, cache: SeqCache, ids_dev: torch.Tensor, n_new: int, keep: list, device_pos: bool) -> _cabi.SeqEntry:
+        nl = len(self.config.layers)
+        pool = self.pool
+        st = (C.c_void_p * nl)(*[(pool.state[i][cache.slot].data_ptr() if pool.state[i] is not None else None) for i in range(nl)])
+        kp = (C.c_void_p * nl)(*[(pool.k[i].data_ptr() if i in pool.k else None) for i in range(nl)])
+        vp = (C.c_void_p * nl)(*[(pool.v[i].data_ptr() if i in pool.v else None) for i in range(nl)])
+        keep += [st, kp, vp]
+        return _cabi.SeqEntry(n_new=n_new, past=cache.seq_len, ids=ids_dev.data_ptr(), page_table=cache.page_table.data_ptr(),
+                              scalars=cache.scalars.data_ptr() if device_pos else None, layer_state=st, k_pages=kp, v_pages=vp)
+
+    @torch.inference_mode()
+    def forward_step(self, entries: Sequence[Tuple[SeqCache, Sequence[int]]], want: Optional[Sequence[Sequence[int]]] = None,
+                     layer_dump: bool = False):
+        """One step of the scheduler: each entry brings a sequence's next tokens (a prompt portion of any length, or one
+        token); `want[e]` lists the places among entry e's tokens whose logits are asked for. Linear layers and row ops run
+        over the rows of all entries at once, the sequence mixers per entry from the state earlier steps left. Returns
+        fp32 logits [sum(len(want[e])), vocab] in entry order (and, with layer_dump, the residual stream after every layer
+        [layers, rows, width])."""
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        if len({id(c) for c, _ in entries}) != len(entries):
+            raise ValueError("the same sequence appears twice in one step")
+        want = want if want is not None else [[] for _ in entries]
+        rows, want_rows, ents, keep = 0, [], [], []
+        all_ids = []
+        for (cache, ids), w in zip(entries, want):
+            if cache.pool is not self.pool or cache.slot is None:
+                raise TypeError("the cache does not belong to this model (or was released)")
+            ids = [int(x) for x in (ids.tolist() if isinstance(ids, torch.Tensor) else ids)]
+            if not ids:
+                raise ValueError("an entry without tokens")
+            if any(not 0 <= k < len(ids) for k in w):
+                raise ValueError("a wanted place outside the entry's tokens")
+            want_rows += [rows + int(k) for k in w]
+            all_ids += ids
+            rows += len(ids)
+        self._ensure_workspace(rows, max(len(want_rows), 1))
+        ids_dev = torch.tensor(all_ids, dtype=torch.int64).to(self.device)
+        r0 = 0
+        for (cache, ids), _w in zip(entries, want):
+            n = len(ids)
+            cache.ensure_tokens(cache.seq_len + n)   # may move the pool: entries are built after all allocations
+            r0 += n
+        r0 = 0
+        for (cache, ids), _w in zip(entries, want):
+            n = len(ids)
+            ents.append(self._entry(cache, ids_dev[r0:r0 + n], n, keep, device_pos=False))
+            r0 += n
+        nw = len(want_rows)
+        want_dev = torch.tensor(want_rows, dtype=torch.int32).to(self.device) if nw else None
+        logits = torch.empty((nw, self.config.vocab), dtype=torch.float32, device=self.device) if nw else None
+        dump = torch.empty((len(self.config.layers), rows, self.config.width), dtype=torch.float32, device=self.device) if layer_dump else None
+        self._native.forward(ents, PAGE_SIZE, want_dev, nw, logits, None, dump)
+        for (cache, ids), _w in zip(entries, want):
+            cache.advance(len(ids))
+        return (logits, dump) if layer_dump else logits
+
+    # -- generation ----------------------------------------------------------------------------------------------------
+    def _sampling(self, repetition_penalty, max_new_tokens, eos_token_id) -> _cabi.Sampling:
+        eos = self.generation_eos if eos_token_id is None else eos_token_id
+        eos = [int(e) for e in (eos if isinstance(eos, (list, tuple)) else [eos])]
+        return _cabi.Sampling(float(repetition_penalty), -1, 0.0, 0.0, eos[0], int(max_new_tokens),
+                              1.0 / float(repetition_penalty), eos[1] if len(eos) > 1 else -1)
+
+    @torch.inference_mode()
+    def generate(self, input_ids: torch.Tensor, past_key_values: Optional[SeqCache] = None, max_new_tokens: int = 16,
+                 repetition_penalty: float = 1.0, eos_token_id=None, do_sample: Optional[bool] = None,
+                 return_dict_in_generate: bool = True, output_logits: bool = False, prefill_chunk: int = 0, **unsupported):
+        """Greedy generation. input_ids: [1, L] = the full id history; the cache decides how many trailing ids are new.
+        The prompt runs as one step (or in portions of `prefill_chunk` tokens), then every token is one decode step
+        followed by the library's token-selection kernel; positions, ids and the stop flag live on the device, the decode
+        step is captured once as a CUDA graph and replayed, and the host synchronises once per call."""
+        if unsupported:
+            raise TypeError(f"generate() got unsupported arguments {sorted(unsupported)}")
+        if do_sample:
+            raise NotImplementedError("the native token selection is greedy")
+        if input_ids is None or input_ids.dim() != 2 or input_ids.shape[0] != 1:
+            raise ValueError("input_ids must be [1, L] (one sequence per call)")
+        if max_new_tokens < 1:
+            raise ValueError("max_new_tokens must be >= 1")
+        cache = past_key_values if past_key_values is not None else self.new_cache()
+        ids = input_ids[0].tolist()
+        L, past = len(ids), cache.seq_len
+        if L <= past:
+            raise ValueError(f"input_ids has {L} ids but the cache already holds {past}")
+        sp = self._sampling(repetition_penalty, max_new_tokens, eos_token_id)
+        V = self.config.vocab
+        # ---- prompt ----
+        new = ids[past:]
+        step = prefill_chunk if prefill_chunk > 0 else len(new)
+        for a in range(0, len(new) - step, step) if step < len(new) else []:
+            self.forward_step([(cache, new[a:a + step])])
+        done = (len(new) - 1) // step * step if step < len(new) else 0
+        last = new[done:]
+        logits = self.forward_step([(cache, last)], [[len(last) - 1]])
+        # ---- first token + decode steps ----
+        cache.ensure_seq_capacity(L + max_new_tokens + 1)
+        cache.ensure_tokens(L + max_new_tokens)
+        cache.seq_buf[:L].copy_(torch.tensor(ids, dtype=torch.int64))
+        cache.scalars.copy_(torch.tensor([L, L, 0, 0, L, 0, 0, 0], dtype=torch.int32))
+        raw = torch.empty((1, V), dtype=torch.float32, device=self.device)
+        raw.copy_(logits)
+        logits_out = [raw[0].clone()] if output_logits else None
+        self._select(raw, cache, sp, advance=0)
+        n_steps = max_new_tokens - 1
+        hist = torch.empty((n_steps, V), dtype=torch.float32, device=self.device) if output_logits and n_steps else None
+        if n_steps:
+            self._run_decode(cache, raw, sp, n_steps, hist)
+        sc = cache.scalars.tolist()                      # the one host sync of the decode phase
+        n_gen = sc[_cabi.SC_N_GENERATED]
+        # the device advanced the position; pages behind the last chunk go back as in a teacher-forced step
+        cache.seq_len = L
+        cache.advance(sc[_cabi.SC_KV_LEN] - L)
+        seq = cache.seq_buf[: L + n_gen].clone().view(1, -1)
+        if output_logits and hist is not None:
+            logits_out += list(hist[: max(n_gen - 1, 0)])
+        self.last_stats = {"prefill_tokens": len(new), "generated": n_gen, "kv_len": cache.seq_len}
+        out = GenerateOutput(sequences=seq, past_key_values=cache, logits=logits_out[:n_gen] if output_logits else None)
+        return out if return_dict_in_generate else out.sequences
+
+    def _select(self, raw: torch.Tensor, cache: SeqCache, sp: _cabi.Sampling, advance: int):
+        self._logits_proc.copy_(raw[0])
+        self.ctx.call("lcc_sample_greedy", _cabi._ptr(raw), _cabi._ptr(self._logits_proc), _cabi._i(self.config.vocab),
+                      _cabi._ptr(cache.seq_buf), _cabi._ptr(cache.scalars), C.byref(sp), _cabi._i(advance), None, None,
+                      _cabi._i(self.config.width), _cabi.Context.stream_ptr())
+
+    def _decode_once(self, cache: SeqCache, raw: torch.Tensor, sp: _cabi.Sampling, keep: list):
+        """One token, all bookkeeping on the device: the step reads the last id (seq[SEQ_LEN - 1]) and the number of cached
+        tokens (KV_LEN) from the sequence's scalars; the selection kernel appends the next id and advances both."""
+        ent = self._entry(cache, cache.seq_buf, 1, keep, device_pos=True)
+        self._native.forward([ent], PAGE_SIZE, self._want0, 1, raw, None, None)
+        self._select(raw, cache, sp, advance=1)
+
+    def _run_decode(self, cache: SeqCache, raw: torch.Tensor, sp: _cabi.Sampling, n_steps: int, hist):
+        if not hasattr(self, "_want0"):
+            self._want0 = torch.zeros(1, dtype=torch.int32, device=self.device)
+        if not self.use_cuda_graph:
+            keep: list = []
+            for i in range(n_steps):
+                self._decode_once(cache, raw, sp, keep)
+                if hist is not None:
+                    hist[i].copy_(raw[0])
+            return
+        key = (self.pool.generation, cache.table_generation, cache.scalars.data_ptr(), cache.seq_buf.data_ptr(),
+               cache.page_table.data_ptr(), cache.slot, self._native.workspace.data_ptr(),
+               sp.repetition_penalty, sp.eos_token_id, sp.eos_token_id2, sp.max_new_tokens)
+        ent = self._graphs.get(key)
+        first = 0
+        if ent is None:
+            if len(self._graphs) > 16:
+                self._graphs.clear()
+            gkeep: list = []
+            graw = torch.empty_like(raw)
+            self._decode_once(cache, graw, sp, gkeep)   # eager once: lazy module loading, kernel attributes
+            if hist is not None:
+                hist[0].copy_(graw[0])
+            first = 1
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g, stream=side, capture_error_mode="thread_local"):
+                    self._decode_once(cache, graw, sp, gkeep)
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            ent = self._graphs[key] = (g, gkeep, graw)
+        g, _, graw = ent
+        for i in range(first, n_steps):
+            g.replay()
+            if hist is not None:
+                hist[i].copy_(graw[0])
