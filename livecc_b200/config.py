@@ -238,8 +238,8 @@ class SeqModelConfig:
                     postln_alpha=self.alpha, embedding=dict(scale=self.embed_scale), logit_softcap=self.logit_softcap)
 
     def validate(self) -> None:
-        if self.width < 2 or self.width % 2:
-            raise ValueError("the sinusoidal position vector needs an even width")
+        if self.width < 1 or self.vocab < 1:
+            raise ValueError("width and vocab must be positive")
         for i, L in enumerate(self.layers):
             if L.type == "mamba2":
                 s = L.ssd

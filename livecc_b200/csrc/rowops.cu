@@ -138,7 +138,7 @@ inline int done() { return cudaGetLastError() == cudaSuccess ? 0 : -100; }
 
 int embed_sinusoid(int dt, const int64_t* ids, const int* seq_len, const void* table, int64_t vocab, float scale,
                    const float* inv_freq, float* x32, void* xa, int S, int W, SeqPos pos, cudaStream_t s) {
-    if (!ids || !table || !inv_freq || !x32 || !xa || S < 1 || W < 2 || (W & 1)) return -2;
+    if (!ids || !table || !inv_freq || !x32 || !xa || S < 1 || W < 1) return -2;
     count_launch();
     if (dt == DT_F32)
         embed_sinusoid_kernel<float><<<S, 256, 0, s>>>(ids, seq_len, (const float*)table, vocab, scale, inv_freq, x32, (float*)xa, S, W, pos);

@@ -123,7 +123,7 @@ extern "C" {
 lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc) {
     if (!ctx || !desc || !desc->layers) return nullptr;
     auto fail = [&](const char* msg) -> lcc_seq_model* { snprintf(ctx->err, sizeof(ctx->err), "lcc_seq_model_create: %s", msg); return nullptr; };
-    if (desc->width < 2 || (desc->width & 1) || desc->vocab < 1 || desc->n_layers < 1) return fail("bad sizes");
+    if (desc->width < 1 || desc->vocab < 1 || desc->n_layers < 1) return fail("bad sizes");
     if (desc->dtype != LCC_DT_BF16 && desc->dtype != LCC_DT_F32) return fail("unknown storage type");
     if (!desc->embed || !desc->inv_freq_f32 || !desc->final_norm_f32 || !desc->head) return fail("missing weights");
     for (int i = 0; i < desc->n_layers; ++i) {

@@ -245,7 +245,7 @@ class SeqStatePool(PageAllocator):
     def acquire_slot(self) -> int:
         if not self.free_slots:
             self._grow_slots(self.num_slots * 2)
-        slot = self.free_slots.pop(0)
+        slot = self.free_slots.pop()      # the slot freed last is used first
         for t in self.state:
             if t is not None:
                 t[slot].zero_()   # a sequence starts from the zero state, whoever used the slot before

@@ -1,0 +1,281 @@
+"""The hybrid sequence models on the GPU against the float64 oracle (tests/seq_oracle.py): every mechanism alone, whole
+prompts against token-by-token decoding, portions down to two tokens, batches against each request alone, pages and
+state slots that are used again, chunk edges and page borders, long decoding, unusual sizes, and greedy generation
+through the engine's own entry point. fp32 storage is compared tightly; bf16 storage within bf16 rounding."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import seq_cases
+import seq_oracle as O
+from livecc_b200.checkpoint import synthetic_seq_tensors, write_safetensors
+from livecc_b200.config import SeqModelConfig
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+_models = {}
+
+
+def model_of(name, dtype="float32", seed=11):
+    from livecc_b200.seq_engine import SeqLMForCausalLM
+
+    key = (name, dtype, seed)
+    if key not in _models:
+        d = seq_cases.CASES[name]
+        cfg = SeqModelConfig.from_json(d)
+        tensors = synthetic_seq_tensors(cfg, seed=seed)
+        _models[key] = (SeqLMForCausalLM.from_state_dict(cfg, tensors, dtype), d, tensors)
+    return _models[key]
+
+
+_oracle = {}
+
+
+def oracle(name, toks, seed=11, **kw):
+    key = (name, tuple(toks), seed, tuple(sorted(kw.items())))
+    if key not in _oracle:
+        _, d, tensors = model_of(name, "float32", seed)
+        _oracle[key] = O.forward(d, tensors, toks, **kw)
+    return _oracle[key]
+
+
+def rel(got, want):
+    """Largest row error: rms(got - want) / rms(want) over the last axis."""
+    got, want = got.double().cpu(), want.double()
+    return float(((got - want).pow(2).mean(-1).sqrt() / want.pow(2).mean(-1).sqrt().clamp_min(1e-30)).max())
+
+
+def run(m, toks, cuts, want_all=True):
+    """One request through forward_step in portions ending at `cuts`; returns the logits of every position."""
+    c = m.new_cache()
+    rows, lo = [], 0
+    for hi in list(cuts) + [len(toks)]:
+        if hi <= lo:
+            continue
+        rows.append(m.forward_step([(c, toks[lo:hi])], [list(range(hi - lo))]).cpu())
+        lo = hi
+    c.release()
+    return torch.cat(rows)
+
+
+F32_TOL = 2e-5
+BF16_TOL = 4e-2
+
+
+# ---- every mechanism alone, and together, against the oracle ------------------------------------------------------------
+@pytest.mark.parametrize("name", ["ssd_only", "parallel_only", "mixed", "odd"])
+def test_whole_prompt_every_layer_matches_the_oracle_fp32(name):
+    m, d, _ = model_of(name)
+    toks = seq_cases.tokens(75, d["vocab"])
+    want_lg, want_layers = oracle(name, toks)
+    c = m.new_cache()
+    lg, dump = m.forward_step([(c, toks)], [list(range(len(toks)))], layer_dump=True)
+    c.release()
+    for li in range(len(d["layers"])):
+        assert rel(dump[li], want_layers[li]) < F32_TOL, f"residual stream after layer {li} ({d['layers'][li]['type']})"
+    assert rel(lg, want_lg) < F32_TOL
+
+
+@pytest.mark.parametrize("name", ["mixed", "odd"])
+def test_bf16_storage_stays_within_rounding_on_both_linear_paths(name, monkeypatch):
+    from livecc_b200.seq_engine import SeqLMForCausalLM
+
+    _, d, tensors = model_of(name)
+    toks = seq_cases.tokens(90, d["vocab"], seed=3)
+    want_lg, _ = oracle(name, toks)
+    outs = []
+    for tc in ("1", "0"):                       # tensor-core GEMM where the shape allows it / CUDA-core kernels only
+        monkeypatch.setenv("LIVECC_B200_SEQ_TC", tc)
+        m = SeqLMForCausalLM.from_state_dict(SeqModelConfig.from_json(d), tensors, "bfloat16")
+        outs.append(run(m, toks, []))
+        assert rel(outs[-1], want_lg) < BF16_TOL
+        assert rel(run(m, toks, [60] + list(range(61, 90))), want_lg) < BF16_TOL
+    assert rel(outs[0], outs[1].double()) < BF16_TOL
+
+
+# ---- prefill against decoding, portions, first tokens ---------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["ssd_only", "parallel_only", "mixed", "odd"])
+def test_token_by_token_decoding_equals_the_whole_prompt(name):
+    m, d, _ = model_of(name)
+    toks = seq_cases.tokens(70, d["vocab"], seed=1)
+    want_lg, _ = oracle(name, toks)
+    assert rel(run(m, toks, range(1, 70)), want_lg) < F32_TOL          # every token alone, from the first one
+    assert rel(run(m, toks, [41] + list(range(42, 70))), want_lg) < F32_TOL
+
+
+@pytest.mark.parametrize("cuts", [[2, 4, 6, 9, 11, 40, 42], [1, 3, 64, 66], [23, 24, 25, 47, 49, 65], [63, 65, 67, 69]])
+def test_portions_of_any_size_down_to_two_tokens(cuts):
+    m, d, _ = model_of("mixed")
+    toks = seq_cases.tokens(80, d["vocab"], seed=2)
+    want_lg, _ = oracle("mixed", toks)
+    assert rel(run(m, toks, cuts), want_lg) < F32_TOL
+
+
+def test_first_tokens_of_a_sequence():
+    m, d, _ = model_of("mixed")
+    for n in (1, 2, 3):
+        toks = seq_cases.tokens(n, d["vocab"], seed=20 + n)
+        assert rel(run(m, toks, []), oracle("mixed", toks)[0]) < F32_TOL
+
+
+# ---- chunk edges and page borders ------------------------------------------------------------------------------------------
+def test_chunk_edges_and_page_borders_in_prompts_and_in_decoding():
+    """Chunks of 40 over pages of 64 with a sharp softmax: positions 39/40/41, 63/64/65 (a page border inside the chunk
+    [40, 80)), 79/80/81, 119/120/121, 127/128/129, once inside a prompt portion and once decoded alone."""
+    m, d, _ = model_of("sharp")
+    toks = seq_cases.tokens(170, d["vocab"], seed=4)
+    want_lg, _ = oracle("sharp", toks)
+    whole = run(m, toks, [])
+    assert rel(whole, want_lg) < F32_TOL
+    # the test's weights do show the faults it is after: an oracle without the sink, or with chunks one token longer or
+    # shorter, is far outside the tolerance
+    assert rel(whole, oracle("sharp", toks, sink=False)[0]) > 100 * F32_TOL
+    assert rel(whole, oracle("sharp", toks, chunk_shift=1)[0]) > 100 * F32_TOL
+    assert rel(whole, oracle("sharp", toks, chunk_shift=-1)[0]) > 100 * F32_TOL
+    edges = [39, 40, 41, 63, 64, 65, 79, 80, 81, 119, 120, 121, 127, 128, 129]
+    decoded = run(m, toks, [30] + list(range(31, 170)))
+    assert rel(decoded[edges], want_lg[edges]) < F32_TOL
+    assert rel(decoded, want_lg) < F32_TOL
+    assert rel(run(m, toks, [39, 41, 64, 79, 82, 120, 128, 130]), want_lg) < F32_TOL
+
+
+def test_a_key_far_back_in_the_recurrent_state_is_still_seen():
+    """State-space layers only, decay rates set close to zero: the logits at the end depend on the first token through the
+    carried state alone, 150 tokens and 110 decode steps later."""
+    from livecc_b200.seq_engine import SeqLMForCausalLM
+
+    d = seq_cases.CASES["ssd_only"]
+    cfg = SeqModelConfig.from_json(d)
+    tensors = synthetic_seq_tensors(cfg, seed=12)
+    for i in range(len(d["layers"])):
+        tensors[f"l{i}.mix.A_log"].fill_(-7.0)
+    m = SeqLMForCausalLM.from_state_dict(cfg, tensors, "float32")
+    toks = seq_cases.tokens(150, d["vocab"], seed=5)
+    other = [(toks[0] + 1) % d["vocab"]] + toks[1:]
+    a, b = O.forward(d, tensors, toks)[0], O.forward(d, tensors, other)[0]
+    assert rel(b[-1:], a[-1:]) > 100 * F32_TOL, "the test's weights forget the first token"
+    assert rel(run(m, toks, [40] + list(range(41, 150))), a) < F32_TOL
+    assert rel(run(m, other, [40] + list(range(41, 150))), b) < F32_TOL
+
+
+# ---- batches, pages and slots that are used again -----------------------------------------------------------------------------
+def test_a_batch_of_unequal_requests_equals_each_alone():
+    m, d, _ = model_of("mixed")
+    reqs = [seq_cases.tokens(n, d["vocab"], seed=30 + n) for n in (57, 9, 130)]
+    alone = [run(m, t, []) for t in reqs]
+    caches = [m.new_cache() for _ in reqs]
+    # step 1: unequal prompt portions; step 2: one decodes, one continues its prompt, one finishes
+    cut = [40, 8, 70]
+    lg1 = m.forward_step([(c, t[:k]) for c, t, k in zip(caches, reqs, cut)], [list(range(k)) for k in cut]).cpu()
+    lg2 = m.forward_step([(c, t[k:]) for c, t, k in zip(caches, reqs, cut)], [list(range(len(t) - k)) for t, k in zip(reqs, cut)]).cpu()
+    o1 = o2 = 0
+    for t, k, want in zip(reqs, cut, alone):
+        got = torch.cat([lg1[o1:o1 + k], lg2[o2:o2 + len(t) - k]])
+        o1, o2 = o1 + k, o2 + len(t) - k
+        assert rel(got, want.double()) < F32_TOL
+        assert rel(got, oracle("mixed", t)[0]) < F32_TOL
+    for c in caches:
+        c.release()
+
+
+def test_slots_and_pages_of_finished_requests_are_used_again():
+    from livecc_b200.seq_engine import SeqLMForCausalLM
+
+    _, d, tensors = model_of("mixed")
+    m = SeqLMForCausalLM.from_state_dict(SeqModelConfig.from_json(d), tensors, "float32", max_tokens=128)   # a pool of 4 pages
+    a, b, c3 = (seq_cases.tokens(n, d["vocab"], seed=40 + n) for n in (140, 90, 33))
+    want_b, want_c = oracle("mixed", b)[0], oracle("mixed", c3)[0]
+    ca = m.new_cache()
+    m.forward_step([(ca, a)])                   # fills pages and leaves a non-zero state behind
+    slot_a, pages_a = ca.slot, [p for p in ca.pages if p is not None]
+    ca.release()
+    cb = m.new_cache()
+    assert cb.slot == slot_a
+    got_b = m.forward_step([(cb, b[:50])], [list(range(50))]).cpu()
+    cc = m.new_cache()                          # a second live request while b is half way
+    got_c = m.forward_step([(cc, c3)], [list(range(len(c3)))]).cpu()
+    got_b = torch.cat([got_b, m.forward_step([(cb, b[50:])], [list(range(40))]).cpu()])
+    assert set(pages_a) & set(p for p in cb.pages + cc.pages if p is not None), "the freed pages were not handed out again"
+    assert rel(got_b, want_b) < F32_TOL and rel(got_c, want_c) < F32_TOL
+    live_before = cb.live_pages()
+    more = seq_cases.tokens(60, d["vocab"], seed=77)
+    m.forward_step([(cb, more)])                # 150 tokens: both chunk sizes have left the first pages
+    assert cb.live_pages() <= live_before and cb.pages[0] is None
+    cb.release(); cc.release()
+    assert len(m.pool.free) == m.pool.num_pages and len(m.pool.free_slots) == m.pool.num_slots
+
+
+# ---- long decoding, generation ---------------------------------------------------------------------------------------------
+def test_long_decoding_stays_on_the_oracle():
+    m, d, _ = model_of("odd")
+    toks = seq_cases.tokens(260, d["vocab"], seed=6)
+    want_lg, _ = oracle("odd", toks)
+    got = run(m, toks, [4] + list(range(5, 260)))
+    assert rel(got, want_lg) < 2 * F32_TOL
+
+
+def test_greedy_generation_through_the_engine_entry_point():
+    m, d, tensors = model_of("mixed")
+    prompt = seq_cases.tokens(37, d["vocab"], seed=8)
+    want = O.greedy(d, tensors, prompt, 20)
+    ids = torch.tensor([prompt])
+    out = m.generate(ids, max_new_tokens=20, output_logits=True)
+    assert out.sequences[0, :37].tolist() == prompt and out.sequences[0, 37:].tolist() == want
+    # the logits of every step are the oracle's for the sequence so far
+    full, _ = oracle("mixed", prompt + want)
+    assert rel(torch.stack(out.logits), full[36:36 + 20]) < F32_TOL
+    assert out.past_key_values.get_seq_length() == 37 + 19       # the last token is selected, not yet run
+    out.past_key_values.release()
+    # eager launches instead of graph replay, and a prompt cut into portions: the same ids
+    m.use_cuda_graph = False
+    try:
+        assert m.generate(ids, max_new_tokens=20, prefill_chunk=5).sequences[0, 37:].tolist() == want
+    finally:
+        m.use_cuda_graph = True
+    # a stop id ends the call early and later steps leave the state alone; a second turn continues from the cache
+    stop = want[6]
+    first = want.index(stop)
+    out = m.generate(ids, max_new_tokens=20, eos_token_id=stop)
+    assert out.sequences[0, 37:].tolist() == want[:first + 1]
+    assert out.past_key_values.get_seq_length() == 37 + first
+    turn2 = out.sequences[0].tolist() + seq_cases.tokens(5, d["vocab"], seed=9)
+    out2 = m.generate(torch.tensor([turn2]), past_key_values=out.past_key_values, max_new_tokens=4)
+    assert out2.sequences[0, len(turn2):].tolist() == O.greedy(d, tensors, turn2, 4)
+    out2.past_key_values.release()
+    bf, _, _ = model_of("mixed", "bfloat16")
+    got = bf.generate(ids, max_new_tokens=8).sequences[0, 37:].tolist()
+    assert len(got) == 8 and all(0 <= t < d["vocab"] for t in got)
+
+
+def test_trace_replay_command_line(tmp_path):
+    d = seq_cases.CASES["mixed"]
+    cfg = SeqModelConfig.from_json(d)
+    tensors = synthetic_seq_tensors(cfg, seed=11)
+    mdir = tmp_path / "model"
+    mdir.mkdir()
+    (mdir / "config.json").write_text(json.dumps(d))
+    write_safetensors(str(mdir / "model.safetensors"), tensors)
+    a, b = seq_cases.tokens(50, d["vocab"], seed=50), seq_cases.tokens(7, d["vocab"], seed=51)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": a[:33], "want": [0, 32]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": a[33:35], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "x", "tokens": a[35:], "want": [14]}], "end": ["x"]},
+             {"step": 3, "entries": [{"id": "y", "tokens": b, "want": [6]}], "end": ["y"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", str(mdir), "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "64"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(4)]
+    assert not (out / "1.f32").exists()
+    import numpy as np
+
+    la, lb = O.forward(d, tensors, a)[0], O.forward(d, tensors, b)[0]
+    g0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4")).reshape(2, -1)
+    g2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4")).reshape(1, -1)
+    g3 = torch.from_numpy(np.fromfile(out / "3.f32", dtype="<f4")).reshape(1, -1)
+    assert rel(g0, la[[0, 32]]) < F32_TOL and rel(g2, la[[49]]) < F32_TOL and rel(g3, lb[[6]]) < F32_TOL
