@@ -321,6 +321,7 @@ typedef struct {
     const void* s_out;         /* [width, inner] */
     const void* l_in;          /* [Hq*dim + G*dim + G*vdim + Hq, width], rows [q | k | v | gate] */
     const float* l_in_bias_f32; /* same length, zeros for the gate rows */
+    const void* l_in_bias;      /* optional copy in the storage type, padded like the matrix rows (tensor-core epilogue) */
     const float *l_qnorm_f32, *l_knorm_f32; /* [Hq*dim], [G*dim] */
     const void* l_out;         /* [width, Hq*vdim] */
     const float* l_branch_norm_f32; /* [width] */
@@ -336,6 +337,8 @@ typedef struct {
 
 typedef struct {
     int32_t width, vocab, n_layers, dtype;
+    int32_t rows_padded8; /* non-zero: every matrix is allocated with its row count rounded up to 8 (zero rows), so that a
+                             ragged projection can run as an 8-aligned tensor-core GEMM into its padded output buffer */
     float eps, alpha, embed_scale, logit_softcap; /* logit_softcap <= 0: none */
     const void* embed;          /* [vocab, width] */
     const float* inv_freq_f32;  /* [width/2]: sinusoidal position frequencies, computed by the host */

@@ -71,7 +71,7 @@ class SeqLayer(C.Structure):
                [("l_scale", C.c_float)] + [(n, C.c_int32) for n in ("r_heads", "r_dim", "r_vdim", "r_rank")] + \
                [("r_tau", C.c_float)] + \
                [(n, C.c_void_p) for n in ("norm1_f32", "norm2_f32", "s_in", "s_conv_w_f32", "s_conv_b_f32", "s_dt_bias_f32",
-                                          "s_a_log_f32", "s_skip_f32", "s_norm_f32", "s_out", "l_in", "l_in_bias_f32",
+                                          "s_a_log_f32", "s_skip_f32", "s_norm_f32", "s_out", "l_in", "l_in_bias_f32", "l_in_bias",
                                           "l_qnorm_f32", "l_knorm_f32", "l_out", "l_branch_norm_f32", "r_in", "r_decay_up",
                                           "r_decay_bias_f32", "r_norm_f32", "r_out", "r_branch_norm_f32", "ff_in", "ff_out")]
 
@@ -79,7 +79,7 @@ class SeqLayer(C.Structure):
 class SeqModelDesc(C.Structure):
     """lcc_seq_model_desc"""
     _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("dtype", C.c_int32),
-                ("eps", C.c_float), ("alpha", C.c_float), ("embed_scale", C.c_float), ("logit_softcap", C.c_float),
+                ("rows_padded8", C.c_int32), ("eps", C.c_float), ("alpha", C.c_float), ("embed_scale", C.c_float), ("logit_softcap", C.c_float),
                 ("embed", C.c_void_p), ("inv_freq_f32", C.c_void_p), ("final_norm_f32", C.c_void_p), ("head", C.c_void_p),
                 ("layers", C.POINTER(SeqLayer))]
 

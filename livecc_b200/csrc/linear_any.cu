@@ -63,9 +63,27 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(const T* __restrict__ 
     }
 }
 
-// Few rows (M <= 8): one warp per output column streams that row of W once; lanes stride over k.
+// Few rows (M <= 8): one warp per output column streams that row of W once with 16-byte loads (scalar loads when K or a
+// row start is not 16-byte aligned); lanes stride over k, each lane keeps one accumulator per row of A.
 constexpr int kRowsMax = 8;
-template <typename T, typename TC>
+template <typename T> struct Vec16;
+template <> struct Vec16<bf16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[8]) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p);
+        const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+    }
+};
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 u = *reinterpret_cast<const float4*>(p);
+        v[0] = u.x; v[1] = u.y; v[2] = u.z; v[3] = u.w;
+    }
+};
+
+template <typename T, typename TC, bool VEC>
 __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int ldw,
                                                           const float* __restrict__ bias, TC* __restrict__ C, int ldc, int M,
                                                           int N, int K) {
@@ -76,11 +94,29 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ 
     float acc[kRowsMax];
 #pragma unroll
     for (int m = 0; m < kRowsMax; ++m) acc[m] = 0.f;
-    for (int k = lane; k < K; k += 32) {
-        const float wv = ldf(w + k);
+    if (VEC) {
+        constexpr int V = Vec16<T>::N;
+#pragma unroll 2
+        for (int k = lane * V; k < K; k += 32 * V) {
+            float wv[V];
+            Vec16<T>::load(w + k, wv);
 #pragma unroll
-        for (int m = 0; m < kRowsMax; ++m)
-            if (m < M) acc[m] = fmaf(ldf(A + (size_t)m * lda + k), wv, acc[m]);
+            for (int m = 0; m < kRowsMax; ++m) {
+                if (m < M) {
+                    float av[V];
+                    Vec16<T>::load(A + (size_t)m * lda + k, av);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) acc[m] = fmaf(av[i], wv[i], acc[m]);
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) {
+            const float wv = ldf(w + k);
+#pragma unroll
+            for (int m = 0; m < kRowsMax; ++m)
+                if (m < M) acc[m] = fmaf(ldf(A + (size_t)m * lda + k), wv, acc[m]);
+        }
     }
 #pragma unroll
     for (int m = 0; m < kRowsMax; ++m) {
@@ -95,8 +131,13 @@ template <typename T, typename TC>
 int launch_linear(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N, int K,
                   cudaStream_t s) {
     if (M <= kRowsMax) {
+        constexpr int V = Vec16<T>::N;
+        const bool vec = (K % V) == 0 && (lda % V) == 0 && (ldw % V) == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0;
         count_launch();
-        linear_rows_kernel<T, TC><<<(N + 7) / 8, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K);
+        if (vec)
+            linear_rows_kernel<T, TC, true><<<(N + 7) / 8, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K);
+        else
+            linear_rows_kernel<T, TC, false><<<(N + 7) / 8, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K);
     } else {
         dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
         count_launch();

@@ -103,14 +103,16 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     } while (0)
 
 // y[M, N] = x[M, K] W^T (+ bias). Large bf16 products with 8-aligned shapes run on the tensor cores; everything else on
-// the CUDA-core kernels. bias_f32 is fp32; the tensor-core epilogue takes a bf16 bias (bias_bf16, may be null).
+// the CUDA-core kernels. bias is fp32; the tensor-core epilogue takes a copy in the storage type (bias_st; without one a
+// biased product stays on the CUDA cores). A ragged N runs on the tensor cores when the matrix rows are padded to 8.
 int linear(const lcc_seq_model* m, const void* x, int ldx, const void* W, const float* bias, void* y, int ldy,
-           bool y_f32, int M, int N, int K, cudaStream_t s) {
-    if (m->use_tc && m->d.dtype == LCC_DT_BF16 && !y_f32 && !bias && M >= 64 && N >= 64 && K >= 64 && (K % 8) == 0 && (N % 8) == 0 &&
-        (ldx % 8) == 0 && (ldy % 8) == 0) {
+           bool y_f32, int M, int N, int K, cudaStream_t s, const void* bias_st = nullptr) {
+    const int Np = m->d.rows_padded8 ? ld8(N) : N;
+    if (m->use_tc && m->d.dtype == LCC_DT_BF16 && !y_f32 && (!bias || bias_st) && M >= 16 && Np >= 32 && K >= 64 && (K % 8) == 0 &&
+        (Np % 8) == 0 && ldy >= Np && (ldx % 8) == 0 && (ldy % 8) == 0) {
         lcc::GemmArgs a;
-        a.A = x; a.B = W; a.C = y; a.M = M; a.N = N; a.K = K; a.lda = ldx; a.ldb = K; a.ldc = ldy;
-        a.bias = nullptr; a.residual = nullptr; a.ldr = 0; a.epi = lcc::EPI_NONE; a.block_n = 0;
+        a.A = x; a.B = W; a.C = y; a.M = M; a.N = Np; a.K = K; a.lda = ldx; a.ldb = K; a.ldc = ldy;
+        a.bias = bias ? bias_st : nullptr; a.residual = nullptr; a.ldr = 0; a.epi = bias ? lcc::EPI_BIAS : lcc::EPI_NONE; a.block_n = 0;
         return lcc::gemm_bf16_tn(a, m->ctx->num_sms, s);
     }
     return lcc::linear_any(m->d.dtype, x, ldx, W, K, bias, y, ldy, y_f32, M, N, K, s);
@@ -255,7 +257,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
         } else {
             // left: chunk-local attention with a sink
             const int ldl = ld8(z.l_proj), ldo = ld8(z.l_o);
-            STEP(linear(m, xa, W, l.l_in, l.l_in_bias_f32, proj, ldl, false, T, z.l_proj, W, s), "attention in-proj");
+            STEP(linear(m, xa, W, l.l_in, l.l_in_bias_f32, proj, ldl, false, T, z.l_proj, W, s, l.l_in_bias), "attention in-proj");
             int r0 = 0;
             for (int e = 0; e < n_entries; ++e) {
                 const lcc_seq_entry& en = entries[e];

@@ -1,0 +1,126 @@
+"""Prefill and decode throughput of the hybrid sequence models at layer sizes that resemble a real model's, beside the
+framework's Qwen2-style decoder (the closest existing model) at equal width, depth and feed-forward size. Random weights.
+Used by `bench.py --arch seq`; every number is timed with CUDA events on the launching stream after warm-up, and the
+weights of every size are larger than L2, so each step streams them from HBM."""
+from __future__ import annotations
+
+import json
+from typing import Dict, List
+
+import torch
+
+from .checkpoint import synthetic_seq_tensors
+from .config import LiveCCConfig, SeqModelConfig, TextConfig, VisionConfig
+
+# name -> (width, layers, feed-forward, attention chunk)
+SIZES = {
+    "w2048": (2048, 8, 5632, 1024),
+    "w4096": (4096, 4, 11008, 1024),
+}
+PATTERN = ("mamba2", "mamba2", "parallel", "mamba2", "mamba2")
+
+
+def seq_config(width: int, n_layers: int, ff: int, chunk: int, vocab: int = 32768) -> SeqModelConfig:
+    """State-space layers with 2x expansion (64-channel heads, 128 states), every third-ish layer a parallel layer with
+    128-wide attention heads (8 query heads per key/value head) beside gated linear attention, feed-forward on the
+    parallel layers."""
+    layers = []
+    for i in range(n_layers):
+        if PATTERN[i % len(PATTERN)] == "mamba2":
+            layers.append({"type": "mamba2", "mlp": None,
+                           "mixer": dict(heads=2 * width // 64, vdim=64, state=128, groups=8, conv=4, norm_groups=8)})
+        else:
+            heads = width // 128
+            layers.append({"type": "parallel", "mlp": {"ff": ff, "kind": "dense"},
+                           "mixer": {"left": dict(heads=heads, kv_heads=max(1, heads // 8), dim=128, vdim=128, mask={"size": chunk},
+                                                  scale=128 ** -0.5),
+                                     "right": dict(heads=width // 256, dim=128, vdim=256, tau=16.0)}})
+    return SeqModelConfig.from_json({"architecture": "Bimopel", "vocab": vocab, "width": width, "layers": layers,
+                                     "norm": {"eps": 1e-5}, "postln_alpha": 2.0, "embedding": {"scale": width ** 0.5},
+                                     "logit_softcap": 30.0})
+
+
+def qwen_config(width: int, n_layers: int, ff: int, vocab: int = 32768) -> LiveCCConfig:
+    heads = width // 128
+    return LiveCCConfig(
+        text_config=TextConfig(hidden_size=width, intermediate_size=ff, num_hidden_layers=n_layers, num_attention_heads=heads,
+                               num_key_value_heads=max(1, heads // 8)),
+        vision_config=VisionConfig(depth=1, embed_dim=320, hidden_size=width, num_heads=4),
+        name=f"qwen2-w{width}-l{n_layers}").with_vocab(vocab)
+
+
+def _ids(n, vocab, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab - 64, (1, n), generator=g)
+
+
+def _median(xs):
+    xs = sorted(xs)
+    return xs[len(xs) // 2]
+
+
+def time_seq(model, prompt_len: int, new_tokens: int, steps: int, warmup: int) -> Dict:
+    pre, dec = [], []
+    for i in range(warmup + steps):
+        out = model.generate(_ids(prompt_len, model.config.vocab, i), max_new_tokens=new_tokens + 1, eos_token_id=-1)
+        out.past_key_values.release()
+        if i >= warmup:
+            pre.append(model.last_stats["prefill_ms"])
+            dec.append(model.last_stats["decode_ms"] / max(model.last_stats["generated"] - 1, 1))
+    return {"prefill_ms": _median(pre), "prefill_tok_s": prompt_len / _median(pre) * 1e3, "decode_ms_per_token": _median(dec),
+            "decode_tok_s": 1e3 / _median(dec)}
+
+
+def time_qwen(model, prompt_len: int, new_tokens: int, steps: int, warmup: int) -> Dict:
+    pre, dec = [], []
+    saved = model.generation_config.eos_token_id
+    model.generation_config.eos_token_id = -1            # random weights: never stop early
+    for i in range(warmup + steps):
+        out = model.generate(input_ids=_ids(prompt_len, model.config.text_config.vocab_size, i), max_new_tokens=new_tokens + 1)
+        out.past_key_values.release()
+        if i >= warmup:
+            st = model.last_stats
+            pre.append(st["prefill_ms"])
+            dec.append(st["decode_ms"] / max(st["generated"] - 1, 1))
+    model.generation_config.eos_token_id = saved
+    return {"prefill_ms": _median(pre), "prefill_tok_s": prompt_len / _median(pre) * 1e3, "decode_ms_per_token": _median(dec),
+            "decode_tok_s": 1e3 / _median(dec)}
+
+
+def run(sizes: List[str], prompt_lens: List[int], new_tokens: int, steps: int, warmup: int, dtype: str = "bfloat16") -> Dict:
+    from .engine import LiveCCB200ForConditionalGeneration
+    from .seq_engine import SeqLMForCausalLM
+
+    out = {}
+    for name in sizes:
+        width, n_layers, ff, chunk = SIZES[name]
+        cfg = seq_config(width, n_layers, ff, chunk)
+        m = SeqLMForCausalLM.from_state_dict(cfg, synthetic_seq_tensors(cfg, seed=7, device="cuda"), dtype,
+                                             max_tokens=max(prompt_lens) + new_tokens + 64)
+        rec = {"weights_gb": round(m.weights.nbytes() / 1e9, 3), "bimopel": {}, "qwen2": {}}
+        for S in prompt_lens:
+            rec["bimopel"][f"S{S}"] = time_seq(m, S, new_tokens, steps, warmup)
+        del m
+        torch.cuda.empty_cache()
+        q = LiveCCB200ForConditionalGeneration.from_synthetic(qwen_config(width, n_layers, ff))
+        rec["qwen2_weights_gb"] = round(q.weights.nbytes() / 1e9, 3)
+        for S in prompt_lens:
+            rec["qwen2"][f"S{S}"] = time_qwen(q, S, new_tokens, steps, warmup)
+        del q
+        torch.cuda.empty_cache()
+        out[name] = rec
+    return out
+
+
+def main(args) -> Dict:
+    """bench.py --arch seq: one JSON line; `value` = decode tokens/s of the first size at the first prompt length."""
+    sizes = [s for s in (args.seq_sizes.split(",") if args.seq_sizes else list(SIZES)) if s in SIZES]
+    lens = [int(x) for x in args.seq_prompt.split(",")]
+    res = run(sizes, lens, args.max_new_tokens if args.max_new_tokens > 16 else 64, args.steps, max(args.warmup, 3))
+    first = res[sizes[0]]["bimopel"][f"S{lens[0]}"]
+    return {"metric": "decode_tokens_per_s", "value": first["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": first["decode_ms_per_token"], "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic (random weights, random ids)", "vs_baseline": None,
+            "config": {"model": f"Bimopel {sizes[0]} beside Qwen2-style decoder of equal width/depth/ff", "global_batch": 1,
+                       "seq_len": lens[0], "parallelism": "1 gpu", "l2": "weights of every size exceed L2"},
+            "sizes": res}

@@ -51,8 +51,14 @@ class SeqWeights:
             used.add(name)
             return t[name]
 
-        def mat(*names):   # rows of several [out, in] matrices stacked into one
-            return torch.cat([get(n).to(torch.float32) for n in names], 0).to(device=device, dtype=dtype).contiguous()
+        def mat(*names):   # rows of several [out, in] matrices stacked into one; row count padded to 8 with zero rows
+            m = torch.cat([get(n).to(torch.float32) for n in names], 0)
+            if m.shape[0] % 8:
+                m = torch.cat([m, torch.zeros((-m.shape[0]) % 8, m.shape[1], dtype=m.dtype, device=m.device)], 0)
+            return m.to(device=device, dtype=dtype).contiguous()
+
+        def shape(name):
+            return tuple(get(name).shape)
 
         def f32(x):
             return x.to(device=device, dtype=torch.float32).contiguous()
@@ -61,7 +67,7 @@ class SeqWeights:
         self.embed = mat("embed")
         self.head = mat("head")
         self.final_norm = f32(get("final.norm"))
-        if self.embed.shape != (cfg.vocab, W) or self.head.shape != (cfg.vocab, W):
+        if shape("embed") != (cfg.vocab, W) or shape("head") != (cfg.vocab, W):
             raise ValueError("embed / head do not have the shape [vocab, width] of config.json")
         i2 = torch.arange(0, W, 2, dtype=torch.float32)
         self.inv_freq = torch.pow(torch.tensor(10000.0, dtype=torch.float32), -i2 / W).to(device)
@@ -73,8 +79,8 @@ class SeqWeights:
                 s = L.ssd
                 m = p + "mix."
                 w["s_in"] = mat(m + "in")
-                if w["s_in"].shape != (s.proj_rows, W):
-                    raise ValueError(f"{m}in has shape {tuple(w['s_in'].shape)}, config.json implies {(s.proj_rows, W)}")
+                if shape(m + "in") != (s.proj_rows, W):
+                    raise ValueError(f"{m}in has shape {shape(m + 'in')}, config.json implies {(s.proj_rows, W)}")
                 w["s_conv_w"] = f32(get(m + "conv"))
                 if w["s_conv_w"].shape != (s.conv_channels, s.conv):
                     raise ValueError(f"{m}conv has shape {tuple(w['s_conv_w'].shape)}, expected {(s.conv_channels, s.conv)}")
@@ -88,9 +94,14 @@ class SeqWeights:
                 l, r = L.left, L.right
                 a, b = p + "mix.left.", p + "mix.right."
                 w["l_in"] = mat(a + "q", a + "k", a + "v", a + "g")
-                w["l_in_bias"] = f32(torch.cat([get(a + "q.b").float(), get(a + "k.b").float(), get(a + "v.b").float(),
-                                                torch.zeros(l.heads)]))
-                if w["l_in"].shape[0] != l.heads * l.dim + l.kv_heads * (l.dim + l.vdim) + l.heads:
+                qb = get(a + "q.b")
+                bias = torch.cat([qb.float(), get(a + "k.b").float(), get(a + "v.b").float(),
+                                  torch.zeros(l.heads + (-(shape(a + "q")[0] + shape(a + "k")[0] + shape(a + "v")[0] + l.heads)) % 8,
+                                              device=qb.device)])
+                w["l_in_bias"] = f32(bias)
+                w["l_in_bias_st"] = bias.to(device=device, dtype=dtype).contiguous()
+                if (shape(a + "q")[0], shape(a + "k")[0], shape(a + "v")[0], shape(a + "g")[0]) != \
+                        (l.heads * l.dim, l.kv_heads * l.dim, l.kv_heads * l.vdim, l.heads):
                     raise ValueError(f"layer {i}: left projections do not match config.json")
                 w["l_qnorm"] = f32(get(a + "q.norm"))
                 w["l_knorm"] = f32(get(a + "k.norm"))
@@ -98,7 +109,8 @@ class SeqWeights:
                 w["l_branch_norm"] = f32(get(a + "out"))
                 r.rank = int(get(b + "a1").shape[0])
                 w["r_in"] = mat(b + "q", b + "k", b + "v", b + "g", b + "a1")
-                if w["r_in"].shape[0] != 2 * r.heads * r.dim + 2 * r.heads * r.vdim + r.rank:
+                if (shape(b + "q")[0], shape(b + "k")[0], shape(b + "v")[0], shape(b + "g")[0]) != \
+                        (r.heads * r.dim, r.heads * r.dim, r.heads * r.vdim, r.heads * r.vdim):
                     raise ValueError(f"layer {i}: right projections do not match config.json")
                 w["r_decay_up"] = mat(b + "a2")
                 w["r_decay_bias"] = f32(get(b + "a2.b"))
@@ -109,7 +121,7 @@ class SeqWeights:
                 w["norm2"] = f32(get(p + "norm2"))
                 w["ff_in"] = mat(p + "mlp.gate", p + "mlp.up")
                 w["ff_out"] = mat(p + "mlp.down")
-                if w["ff_in"].shape != (2 * L.ff, W):
+                if shape(p + "mlp.gate") != (L.ff, W) or shape(p + "mlp.up") != (L.ff, W):
                     raise ValueError(f"layer {i}: feed-forward width does not match config.json")
             self.layers.append(w)
         self.unused = sorted(set(t) - used)
@@ -178,6 +190,7 @@ class SeqLMForCausalLM:
                 e.l_heads, e.l_kv_heads, e.l_dim, e.l_vdim, e.l_chunk, e.l_scale = l.heads, l.kv_heads, l.dim, l.vdim, l.chunk, l.scale
                 e.r_heads, e.r_dim, e.r_vdim, e.r_rank, e.r_tau = r.heads, r.dim, r.vdim, r.rank, r.tau
                 e.l_in, e.l_in_bias_f32, e.l_qnorm_f32, e.l_knorm_f32 = p(lw["l_in"]), p(lw["l_in_bias"]), p(lw["l_qnorm"]), p(lw["l_knorm"])
+                e.l_in_bias = p(lw["l_in_bias_st"])
                 e.l_out, e.l_branch_norm_f32 = p(lw["l_out"]), p(lw["l_branch_norm"])
                 e.r_in, e.r_decay_up, e.r_decay_bias_f32 = p(lw["r_in"]), p(lw["r_decay_up"]), p(lw["r_decay_bias"])
                 e.r_norm_f32, e.r_out, e.r_branch_norm_f32 = p(lw["r_norm"]), p(lw["r_out"]), p(lw["r_branch_norm"])
@@ -185,7 +198,7 @@ class SeqLMForCausalLM:
                 e.norm2_f32, e.ff_in, e.ff_out = p(lw["norm2"]), p(lw["ff_in"]), p(lw["ff_out"])
         desc = _cabi.SeqModelDesc(
             width=cfg.width, vocab=cfg.vocab, n_layers=len(cfg.layers),
-            dtype=_cabi.DT_F32 if self.dtype == torch.float32 else _cabi.DT_BF16, eps=cfg.eps, alpha=cfg.alpha,
+            dtype=_cabi.DT_F32 if self.dtype == torch.float32 else _cabi.DT_BF16, rows_padded8=1, eps=cfg.eps, alpha=cfg.alpha,
             embed_scale=cfg.embed_scale, logit_softcap=cfg.logit_softcap, embed=p(w.embed), inv_freq_f32=p(w.inv_freq),
             final_norm_f32=p(w.final_norm), head=p(w.head), layers=arr)
         return _cabi.SeqNativeModel(self.ctx, desc, keepalive=(arr, w))
@@ -299,6 +312,8 @@ class SeqLMForCausalLM:
             raise ValueError(f"input_ids has {L} ids but the cache already holds {past}")
         sp = self._sampling(repetition_penalty, max_new_tokens, eos_token_id)
         V = self.config.vocab
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        ev[0].record()
         # ---- prompt ----
         new = ids[past:]
         step = prefill_chunk if prefill_chunk > 0 else len(new)
@@ -318,8 +333,10 @@ class SeqLMForCausalLM:
         self._select(raw, cache, sp, advance=0)
         n_steps = max_new_tokens - 1
         hist = torch.empty((n_steps, V), dtype=torch.float32, device=self.device) if output_logits and n_steps else None
+        ev[1].record()
         if n_steps:
             self._run_decode(cache, raw, sp, n_steps, hist)
+        ev[2].record()
         sc = cache.scalars.tolist()                      # the one host sync of the decode phase
         n_gen = sc[_cabi.SC_N_GENERATED]
         # the device advanced the position; pages behind the last chunk go back as in a teacher-forced step
@@ -328,7 +345,8 @@ class SeqLMForCausalLM:
         seq = cache.seq_buf[: L + n_gen].clone().view(1, -1)
         if output_logits and hist is not None:
             logits_out += list(hist[: max(n_gen - 1, 0)])
-        self.last_stats = {"prefill_tokens": len(new), "generated": n_gen, "kv_len": cache.seq_len}
+        self.last_stats = {"prefill_tokens": len(new), "generated": n_gen, "kv_len": cache.seq_len,
+                           "prefill_ms": ev[0].elapsed_time(ev[1]), "decode_ms": ev[1].elapsed_time(ev[2])}
         out = GenerateOutput(sequences=seq, past_key_values=cache, logits=logits_out[:n_gen] if output_logits else None)
         return out if return_dict_in_generate else out.sequences
 
