@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(256) qk_norm_kv_append_kernel(const T* __restr
     }
 }
 
-// One CTA per (new row, query head). Scores of the row's chunk go to shared memory (fp32), then the weights, then
+// Decode steps and portions of fewer than kAttnTiledMin rows: one CTA per (new row, query head). Scores of the row's chunk go to shared memory (fp32), then the weights, then
 // thread c accumulates output channel c over the keys.
 template <typename T>
 __global__ void __launch_bounds__(128) attn_chunk_sink_kernel(const float* __restrict__ q, const T* __restrict__ k_pages,
@@ -112,6 +112,135 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_kernel(const float* __res
     }
 }
 
+// Prompt portions: one CTA per (64 query rows, query head, 128 output channels). Keys are walked in tiles of 64 from the
+// start of the chunk of the tile's first row to its last row; scores are a register-tiled fp32 product (4 x 4 per thread)
+// staged through shared memory in slices of 16 head channels, the softmax is the running (max, sum) form started at
+// max = 0, sum = 1, which is exactly the sink's term, and the weights go through shared memory into the product with V.
+constexpr int AQ = 64, AK = 64, ADS = 16, AVW = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pages,
+                                                                    const T* __restrict__ v_pages, const int* __restrict__ page_table,
+                                                                    int page_size, const T* __restrict__ gate, int ld_gate,
+                                                                    T* __restrict__ out, int ld_out, int S, int Hq, int G, int D, int DV,
+                                                                    int chunk, float scale, SeqPos pos) {
+    if (seq_done(pos)) return;
+    __shared__ float sq_[ADS][AQ + 4], sk_[ADS][AK + 4];
+    __shared__ float sp_[AK][AQ + 4];
+    __shared__ float sv_[ADS][AVW + 4];
+    const int t0 = blockIdx.x * AQ, h = blockIdx.y, c0 = blockIdx.z * AVW;
+    const int g = h / (Hq / G);
+    const int past = seq_past(pos, S);
+    const int rows = min(AQ, S - t0);
+    const int pf = past + t0, pl = pf + rows - 1;
+    const int kbeg = chunk > 0 ? (pf / chunk) * chunk : 0;
+    const int tm = (threadIdx.x / 16) * 4, tn = (threadIdx.x % 16) * 4;
+    int p_row[4], lo_row[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        p_row[i] = pf + tm + i;
+        lo_row[i] = chunk > 0 ? (p_row[i] / chunk) * chunk : 0;
+    }
+    float m[4] = {0.f, 0.f, 0.f, 0.f}, l[4] = {1.f, 1.f, 1.f, 1.f};
+    float o[4][8] = {};
+    const float* qh = q + ((size_t)t0 * Hq + h) * D;
+    for (int k0 = kbeg; k0 <= pl; k0 += AK) {
+        float sc[4][4] = {};
+        for (int d0 = 0; d0 < D; d0 += ADS) {
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < AQ * ADS / 256; ++i) {
+                const int e = threadIdx.x + i * 256, r = e / ADS, kk = e % ADS, d = d0 + kk;
+                sq_[kk][r] = (r < rows && d < D) ? qh[(size_t)r * Hq * D + d] : 0.f;
+                const int pj = k0 + r;
+                float kv = 0.f;
+                if (pj <= pl && d < D)
+                    kv = ldf(k_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * D + d);
+                sk_[kk][r] = kv;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int kk = 0; kk < ADS; ++kk) {
+                const float4 av = *reinterpret_cast<const float4*>(&sq_[kk][tm]);
+                const float4 bv = *reinterpret_cast<const float4*>(&sk_[kk][tn]);
+                const float a[4] = {av.x, av.y, av.z, av.w}, b[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) sc[i][j] = fmaf(a[i], b[j], sc[i][j]);
+            }
+        }
+        // running softmax; the 16 threads that share a row are 16 neighbouring lanes of one warp
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int pj = k0 + tn + j;
+                const bool ok = pj <= p_row[i] && pj >= lo_row[i] && tm + i < rows;
+                sc[i][j] = ok ? sc[i][j] * scale : -INFINITY;
+                mx = fmaxf(mx, sc[i][j]);
+            }
+#pragma unroll
+            for (int w = 8; w > 0; w >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, w));
+            const float mn = fmaxf(m[i], mx);          // finite: m starts at the sink's score
+            const float corr = expf(m[i] - mn);
+            float rs = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float pw = expf(sc[i][j] - mn);  // exp(-inf) = 0 for masked keys
+                sp_[tn + j][tm + i] = pw;
+                rs += pw;
+            }
+#pragma unroll
+            for (int w = 8; w > 0; w >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, w);
+            l[i] = fmaf(l[i], corr, rs);
+            m[i] = mn;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) o[i][c] *= corr;
+        }
+        for (int j0 = 0; j0 < AK; j0 += ADS) {
+            if (k0 + j0 > pl) break;                   // uniform over the CTA
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < ADS * AVW / 256; ++i) {
+                const int e = threadIdx.x + i * 256, kk = e / AVW, c = e % AVW;
+                const int pj = k0 + j0 + kk;
+                float vv = 0.f;
+                if (pj <= pl && c0 + c < DV)
+                    vv = ldf(v_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * DV + c0 + c);
+                sv_[kk][c] = vv;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int kk = 0; kk < ADS; ++kk) {
+                const float4 av = *reinterpret_cast<const float4*>(&sp_[j0 + kk][tm]);
+                const float4 b0 = *reinterpret_cast<const float4*>(&sv_[kk][tn]);
+                const float4 b1 = *reinterpret_cast<const float4*>(&sv_[kk][64 + tn]);
+                const float a[4] = {av.x, av.y, av.z, av.w};
+                const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) o[i][c] = fmaf(a[i], b[c], o[i][c]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t = t0 + tm + i;
+        if (tm + i >= rows) continue;
+        float gv = 1.f;
+        if (gate) gv = 1.f / (1.f + expf(-ldf(gate + (size_t)t * ld_gate + h)));
+        const float f = gv / l[i];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int col = c0 + (c < 4 ? tn + c : 64 + tn + c - 4);
+            if (col < DV) stf(out + (size_t)t * ld_out + (size_t)h * DV + col, o[i][c] * f);
+        }
+    }
+}
+
 }  // namespace
 
 int qk_norm_kv_append(int dt, const void* proj, int ld, const float* qn_w, const float* kn_w, float eps, float* q_out,
@@ -135,6 +264,19 @@ int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_p
                     int DV, int chunk, float scale, SeqPos pos, cudaStream_t s) {
     if (!q || !k_pages || !v_pages || !page_table || !out || S < 1 || Hq < 1 || G < 1 || Hq % G || D < 1 || DV < 1)
         return -2;
+    if (S >= kAttnTiledMin) {
+        dim3 grid((S + AQ - 1) / AQ, Hq, (DV + AVW - 1) / AVW);
+        count_launch();
+        if (dt == DT_F32)
+            attn_chunk_sink_tiled_kernel<float><<<grid, 256, 0, s>>>(q, (const float*)k_pages, (const float*)v_pages, page_table,
+                                                                     page_size, (const float*)gate, ld_gate, (float*)out, ld_out,
+                                                                     S, Hq, G, D, DV, chunk, scale, pos);
+        else
+            attn_chunk_sink_tiled_kernel<bf16><<<grid, 256, 0, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table,
+                                                                    page_size, (const bf16*)gate, ld_gate, (bf16*)out, ld_out, S,
+                                                                    Hq, G, D, DV, chunk, scale, pos);
+        return cudaGetLastError() == cudaSuccess ? 0 : -100;
+    }
     // shared memory holds one score per key of the longest window a row of this call can have
     int max_keys = chunk;
     if (chunk <= 0) {

@@ -72,7 +72,7 @@ __global__ void ssm_step_decay_kernel(const T* __restrict__ raw, int ld, const f
     const int t = i / heads, h = i % heads;
     const float dt = softplus_f(ldf(raw + (size_t)t * ld + h) + dt_bias[h]);
     dt_out[i] = dt;
-    decay_out[i] = expf(-expf(a_log[h]) * dt);
+    decay_out[i] = -expf(a_log[h]) * dt;
 }
 
 template <typename T>
@@ -82,9 +82,9 @@ __global__ void gla_decay_kernel(const T* __restrict__ z, int ld, const float* _
     if (i >= S * n) return;
     const int t = i / n, c = i % n;
     const float x = ldf(z + (size_t)t * ld + c) + (bias ? bias[c] : 0.f);
-    // log(sigmoid(x)) = min(x, 0) - log1p(exp(-|x|)); the decay is its exponential scaled by 1/tau
+    // log(sigmoid(x)) = min(x, 0) - log1p(exp(-|x|)); the log decay is that over tau
     const float ls = fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
-    decay_out[i] = expf(ls * inv_tau);
+    decay_out[i] = ls * inv_tau;
 }
 
 // ---- gated linear recurrence --------------------------------------------------------------------------------------------
@@ -132,10 +132,10 @@ __global__ void __launch_bounds__(kScanThreads) gated_scan_kernel(ScanArgs a, Se
             const int t = e / N, n = e % N;
             sk[e] = ldf(gk + (size_t)(t0 + t) * a.ld_k + n);
             scv[e] = ldf(gc + (size_t)(t0 + t) * a.ld_c + n) * a.cs;
-            if (VEC) sd[e] = a.a[((size_t)(t0 + t) * a.heads + h) * N + n];
+            if (VEC) sd[e] = expf(a.a[((size_t)(t0 + t) * a.heads + h) * N + n]);
         }
         for (int e = tid; e < nt; e += nthr) {
-            if (!VEC) sd[e] = a.a[(size_t)(t0 + e) * a.heads + h];
+            if (!VEC) sd[e] = expf(a.a[(size_t)(t0 + e) * a.heads + h]);
             ssc[e] = a.sc ? a.sc[(size_t)(t0 + e) * a.heads + h] : 1.f;
         }
         for (int e = tid; e < nt * cols; e += nthr) {
@@ -218,6 +218,7 @@ int gated_scan(const ScanArgs& a, SeqPos pos, cudaStream_t s) {
     if (!a.k || !a.c || !a.u || !a.a || !a.state || !a.y || a.S < 1 || a.heads < 1 || a.N < 1 || a.P < 1 ||
         a.heads_per_group < 1)
         return -2;
+    if (a.ws && a.S >= kScanChunkedMin && !pos.kv_len) return gated_scan_chunked(a, pos, s);
     int JP = 1;
     while (JP * NT < a.N) JP *= 2;
     if (JP > 32) return -3;  // N <= 512

@@ -54,7 +54,7 @@ Dims dims_of(const lcc_seq_layer& L) {
 inline int ld8(int n) { return (n + 7) / 8 * 8; }
 
 struct WsLayout {
-    size_t x32, xa, proj, proj2, mid, mid2, y32, q32, f1, f2, o1, o2, xf, total;
+    size_t x32, xa, proj, proj2, mid, mid2, y32, q32, f1, f2, o1, o2, xf, scan, scan_floats, total;
     int w_proj, w_proj2, w_mid, w_y, w_q, w_f;
 };
 
@@ -63,15 +63,18 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     const size_t es = lcc::dt_size(m->d.dtype);
     const size_t nt = NT > 0 ? NT : 1, nw = NW > 0 ? NW : 1;
     int wp = 8, wp2 = 8, wm = 8, wy = 8, wq = 8, wf = 8;
+    size_t scan_floats = 0;
     for (const lcc_seq_layer& l : m->layers) {
         const Dims z = dims_of(l);
         if (l.type == LCC_MIX_SSD) {
             wp = std::max(wp, ld8(z.s_proj)); wm = std::max(wm, ld8(std::max(z.conv_ch, z.inner)));
             wy = std::max(wy, z.inner); wf = std::max(wf, l.s_heads);
+            scan_floats = std::max(scan_floats, lcc::gated_scan_ws_floats(NT, l.s_heads, l.s_state, l.s_vdim));
         } else {
             wp = std::max(wp, ld8(std::max(z.l_proj, z.r_proj))); wp2 = std::max(wp2, ld8(z.r_nk));
             wm = std::max(wm, ld8(std::max(z.l_o, z.r_nv)));
             wy = std::max(wy, z.r_nv); wq = std::max(wq, z.l_nq); wf = std::max(wf, z.r_nk);
+            scan_floats = std::max(scan_floats, lcc::gated_scan_ws_floats(NT, l.r_heads, l.r_dim, l.r_vdim));
         }
         if (l.ff > 0) { wp = std::max(wp, ld8(2 * l.ff)); wm = std::max(wm, ld8(l.ff)); }
     }
@@ -92,6 +95,8 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     L.o1 = take(nt * ld8(W) * es);
     L.o2 = take(nt * ld8(W) * es);
     L.xf = take(nw * ld8(W) * es);
+    L.scan_floats = NT >= lcc::kScanChunkedMin ? scan_floats : 0;   // a decode-only workspace has no use for it
+    L.scan = take(L.scan_floats * 4);
     L.total = off;
     return L;
 }
@@ -202,6 +207,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
     float* y32 = (float*)(ws + L.y32); float* q32 = (float*)(ws + L.q32);
     float* f1 = (float*)(ws + L.f1); float* f2 = (float*)(ws + L.f2);
     uint8_t* o1 = ws + L.o1; uint8_t* o2 = ws + L.o2; uint8_t* xf = ws + L.xf;
+    float* scan_ws = L.scan_floats ? (float*)(ws + L.scan) : nullptr;
     auto pos_of = [&](const lcc_seq_entry& e) {
         lcc::SeqPos p{e.past, nullptr, nullptr};
         if (e.scalars) { p.kv_len = e.scalars + LCC_SC_KV_LEN; p.finished = e.scalars + LCC_SC_FINISHED; }
@@ -246,6 +252,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                 a.state = st + (size_t)z.conv_ch * (l.s_conv - 1);
                 a.y = y32 + (size_t)r0 * z.inner; a.ld_y = z.inner;
                 a.S = en.n_new; a.heads = l.s_heads; a.heads_per_group = l.s_heads / l.s_groups; a.N = l.s_state; a.P = l.s_vdim;
+                a.ws = scan_ws; a.ws_floats = L.scan_floats;
                 STEP(lcc::gated_scan(a, pos, s), "state-space recurrence");
                 r0 += en.n_new;
             }
@@ -296,6 +303,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                 a.state = st;
                 a.y = y32 + (size_t)r0 * z.r_nv; a.ld_y = z.r_nv;
                 a.S = en.n_new; a.heads = l.r_heads; a.heads_per_group = 1; a.N = l.r_dim; a.P = l.r_vdim;
+                a.ws = scan_ws; a.ws_floats = L.scan_floats;
                 STEP(lcc::gated_scan(a, pos_of(en), s), "linear-attention recurrence");
                 r0 += en.n_new;
             }

@@ -38,33 +38,42 @@ int linear_any(int dt, const void* A, int lda, const void* W, int ldw, const flo
 int causal_conv_silu(int dt, const void* in, int ld_in, void* out, int ld_out, const float* w, const float* b,
                      float* carry, int S, int C, int taps, SeqPos pos, cudaStream_t s);
 
-// Step sizes and decays of a scalar-decay state-space layer: dt = softplus(raw + dt_bias[h]), decay = exp(-exp(a_log[h]) * dt).
-// raw: [S, heads] slice (storage dt, leading dimension ld); dt_out / decay_out: fp32 [S, heads].
+// Step sizes and log decays of a scalar-decay state-space layer: dt = softplus(raw + dt_bias[h]),
+// log decay = -exp(a_log[h]) * dt. raw: [S, heads] slice (storage dt, leading dimension ld); dt_out / decay_out: fp32 [S, heads].
 int ssm_step_decay(int dt, const void* raw, int ld, const float* dt_bias, const float* a_log, float* dt_out,
                    float* decay_out, int S, int heads, cudaStream_t s);
-// Per-channel decays of gated linear attention: decay = sigmoid(z + bias)^(1/tau); z: [S, n] slice (storage dt).
+// Per-channel log decays of gated linear attention: log(sigmoid(z + bias)) / tau; z: [S, n] slice (storage dt).
 int gla_decay(int dt, const void* z, int ld, const float* bias, float tau, float* decay_out, int S, int n,
               cudaStream_t s);
 
 // Gated linear recurrence, one state matrix St[n, p] (n < N key channels, p < P value channels) per head:
 //     St <- diag(a_t) St + k_t (sc_t * u_t)^T ,   y_t = St^T (cs * c_t) + skip[h] * u_t
 // k, c: [S, *] slices with head-group stride (head h reads columns (h / heads_per_group) * N + n); u: [S, heads*P] slice;
-// a: fp32, either [S, heads] (vec_decay = 0) or [S, heads*N]; sc: fp32 [S, heads] or null (= 1); skip: fp32 [heads] or null.
-// state: fp32 [heads, P, N] (n fastest), read at the start and written back at the end. y: fp32 [S, heads*P].
+// a: fp32 log decays (log a_t <= 0), either [S, heads] (vec_decay = 0) or [S, heads*N]; sc: fp32 [S, heads] or null (= 1);
+// skip: fp32 [heads] or null. state: fp32 [heads, P, N] (n fastest), read at the start and written back at the end.
+// y: fp32 [S, heads*P]. Two forms compute it: a token-by-token kernel (decode steps and short portions), and, for portions
+// of kScanChunkedMin rows or more when a workspace is given, a sequence-parallel form over blocks of 64 rows
+// (recurrent_chunked.cu), which overwrites `a` with block-local cumulative sums.
 struct ScanArgs {
     int dt;
     const void* k; int ld_k;
     const void* c; int ld_c;
     const void* u; int ld_u;
-    const float* a; int vec_decay;
+    float* a; int vec_decay;
     const float* sc;
     const float* skip;
     float cs;
     float* state;
     float* y; int ld_y;
     int S, heads, heads_per_group, N, P;
+    float* ws; size_t ws_floats;   // workspace of the sequence-parallel form (null: token by token)
 };
+constexpr int kScanChunkedMin = 32;     // rows from which the sequence-parallel form runs
+constexpr int kScanMaxBlocks = 64;      // blocks of 64 rows per pass of the sequence-parallel form (bounds its workspace)
 int gated_scan(const ScanArgs& a, SeqPos pos, cudaStream_t s);
+int gated_scan_chunked(const ScanArgs& a, SeqPos pos, cudaStream_t s);
+// fp32 elements of workspace that let a call of S rows run in the fewest passes
+size_t gated_scan_ws_floats(int S, int heads, int N, int P);
 
 // ---- attn_local.cu ------------------------------------------------------------------------------------------------------
 // RMS norm of the whole q projection and of the whole k projection of each row (weights qn_w [Hq*D], kn_w [G*D], fp32),
@@ -78,6 +87,7 @@ int qk_norm_kv_append(int dt, const void* proj, int ld, const float* qn_w, const
 // floor(j / chunk) == floor(i / chunk); weights exp(s_j) / (1 + sum_j exp(s_j)) (a sink with score 0 and no value);
 // head h's output is multiplied by sigmoid(gate[h]). q: fp32 [S, Hq*D]; gate: [S, Hq] slice (storage dt, leading dim
 // ld_gate) or null; out: [S, Hq*DV] (storage dt). chunk <= 0 means one chunk (plain causal attention).
+constexpr int kAttnTiledMin = 16;   // rows from which the tiled kernel runs (below: one CTA per row and head)
 int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_pages, const int* page_table,
                     int page_size, const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D,
                     int DV, int chunk, float scale, SeqPos pos, cudaStream_t s);

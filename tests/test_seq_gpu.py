@@ -163,6 +163,52 @@ def test_a_key_far_back_in_the_recurrent_state_is_still_seen():
     assert rel(run(m, other, [40] + list(range(41, 150))), b) < F32_TOL
 
 
+# ---- the sequence-parallel kernels of prompt portions ----------------------------------------------------------------------
+def _check_long(d, tensors, n, cuts, seed, tol=F32_TOL):
+    from livecc_b200.seq_engine import SeqLMForCausalLM
+
+    m = SeqLMForCausalLM.from_state_dict(SeqModelConfig.from_json(d), tensors, "float32")
+    toks = seq_cases.tokens(n, d["vocab"], seed=seed)
+    want_lg, want_layers = O.forward(d, tensors, toks)
+    c = m.new_cache()
+    lg, dump = m.forward_step([(c, toks)], [list(range(n))], layer_dump=True)
+    c.release()
+    for li in range(len(d["layers"])):
+        assert rel(dump[li], want_layers[li]) < tol, f"residual stream after layer {li}"
+    assert rel(lg, want_lg) < tol
+    assert rel(run(m, toks, cuts), want_lg) < tol
+
+
+def test_long_prompts_cross_many_blocks_of_the_recurrence_and_key_tiles():
+    """333 tokens: five full 64-row blocks of the recurrence and a ragged sixth, attention chunks of 24 and 10 that never
+    line up with the 64-key tiles; then portions that start and end inside blocks (the carried state enters mid-way)."""
+    _, d, tensors = model_of("mixed")
+    _check_long(d, tensors, 333, [100, 131, 133, 260, 292], seed=50)
+
+
+def test_strong_and_weak_decays_in_the_block_form():
+    """Decays near zero (a row forgets everything before it within a few tokens: the block form must not overflow where
+    it divides cumulative decays) and near one, mixed over channels and heads."""
+    d = seq_cases.CASES["odd"]
+    cfg = SeqModelConfig.from_json(d)
+    tensors = synthetic_seq_tensors(cfg, seed=13)
+    b = tensors["l0.mix.right.a2.b"]
+    b.copy_(torch.linspace(-60.0, 12.0, b.numel()).to(b.dtype))          # tau = 1: log decay down to -60 per token
+    tensors["l1.mix.A_log"].copy_(torch.tensor([3.0, -6.0]).to(tensors["l1.mix.A_log"].dtype))
+    tensors["l1.mix.dt_bias"].copy_(torch.tensor([4.0, 0.0]).to(tensors["l1.mix.dt_bias"].dtype))
+    _check_long(d, tensors, 200, [70, 137], seed=51, tol=2 * F32_TOL)
+
+
+def test_heads_wider_than_one_tile():
+    """Key, value and state sizes above 64 and 128 (several tiles per head, ragged last tiles), one chunk that is longer
+    than a key tile and one that is shorter, a long chunk whose last key tile ends on the row itself."""
+    layers = [seq_cases.par(heads=2, kv_heads=1, dim=72, vdim=136, chunk=150, scale=0.2, r_heads=1, r_dim=70, r_vdim=67, tau=8.0, ff=None),
+              seq_cases.ssd(heads=2, vdim=66, state=68, groups=1, conv=3, norm_groups=2)]
+    d = seq_cases.config(layers, width=32, vocab=64)
+    tensors = synthetic_seq_tensors(SeqModelConfig.from_json(d), seed=14)
+    _check_long(d, tensors, 215, [64, 128, 129, 193], seed=52)
+
+
 # ---- batches, pages and slots that are used again -----------------------------------------------------------------------------
 def test_a_batch_of_unequal_requests_equals_each_alone():
     m, d, _ = model_of("mixed")
