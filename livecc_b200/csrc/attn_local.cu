@@ -113,10 +113,29 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_kernel(const float* __res
 }
 
 // Prompt portions: one CTA per (64 query rows, query head, 128 output channels). Keys are walked in tiles of 64 from the
-// start of the chunk of the tile's first row to its last row; scores are a register-tiled fp32 product (4 x 4 per thread)
-// staged through shared memory in slices of 16 head channels, the softmax is the running (max, sum) form started at
-// max = 0, sum = 1, which is exactly the sink's term, and the weights go through shared memory into the product with V.
-constexpr int AQ = 64, AK = 64, ADS = 16, AVW = 128;
+// start of the chunk of the tile's first row to its last row. Per key tile the CTA stages the K tile (up to 128 head
+// channels at a time) and the V tile into shared memory in the storage type with all its loads in flight together, forms
+// the scores as a register-tiled fp32 product (4 x 4 per thread; the fp32 queries are staged once), runs the softmax in
+// the running (max, sum) form started at max = 0, sum = 1, which is exactly the sink's term, and passes the weights
+// through shared memory into the product with V (4 x 8 per thread).
+constexpr int AQ = 64, AK = 64, ADC = 128, AVW = 128, APQ = AQ + 4, APV = AVW + 4;
+
+template <typename T> __device__ __forceinline__ void ld4(const T* p, float (&v)[4]);
+template <> __device__ __forceinline__ void ld4<float>(const float* p, float (&v)[4]) {
+    const float4 u = *reinterpret_cast<const float4*>(p);
+    v[0] = u.x; v[1] = u.y; v[2] = u.z; v[3] = u.w;
+}
+template <> __device__ __forceinline__ void ld4<bf16>(const bf16* p, float (&v)[4]) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
+template <typename T>
+size_t attn_tiled_smem(int D) {
+    const size_t dc = D < ADC ? D : ADC;
+    return dc * APQ * 4 + dc * APQ * sizeof(T) + (size_t)AK * APV * sizeof(T) + (size_t)AK * APQ * 4;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float* __restrict__ q, const T* __restrict__ k_pages,
@@ -125,16 +144,21 @@ __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float*
                                                                     T* __restrict__ out, int ld_out, int S, int Hq, int G, int D, int DV,
                                                                     int chunk, float scale, SeqPos pos) {
     if (seq_done(pos)) return;
-    __shared__ float sq_[ADS][AQ + 4], sk_[ADS][AK + 4];
-    __shared__ float sp_[AK][AQ + 4];
-    __shared__ float sv_[ADS][AVW + 4];
-    const int t0 = blockIdx.x * AQ, h = blockIdx.y, c0 = blockIdx.z * AVW;
+    extern __shared__ __align__(16) uint8_t smem_attn[];
+    const int dc = min(D, ADC);
+    float* sq_ = reinterpret_cast<float*>(smem_attn);                     // [dc][APQ]
+    float* sp_ = sq_ + (size_t)dc * APQ;                                  // [AK][APQ]
+    T* sk_ = reinterpret_cast<T*>(sp_ + (size_t)AK * APQ);                // [dc][APQ]
+    T* sv_ = sk_ + (size_t)dc * APQ;                                      // [AK][APV]
+    // heavy (late) query tiles first: a tile's work grows with its distance from the start of its chunk
+    const int t0 = (gridDim.x - 1 - blockIdx.x) * AQ, h = blockIdx.y, c0 = blockIdx.z * AVW;
     const int g = h / (Hq / G);
     const int past = seq_past(pos, S);
     const int rows = min(AQ, S - t0);
     const int pf = past + t0, pl = pf + rows - 1;
     const int kbeg = chunk > 0 ? (pf / chunk) * chunk : 0;
     const int tm = (threadIdx.x / 16) * 4, tn = (threadIdx.x % 16) * 4;
+    const int lr = threadIdx.x / 16, lc = threadIdx.x % 16;              // staging: 16 threads walk a row
     int p_row[4], lo_row[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -144,26 +168,56 @@ __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float*
     float m[4] = {0.f, 0.f, 0.f, 0.f}, l[4] = {1.f, 1.f, 1.f, 1.f};
     float o[4][8] = {};
     const float* qh = q + ((size_t)t0 * Hq + h) * D;
+    const bool q_once = D <= ADC;
+    bool q_staged = false;
     for (int k0 = kbeg; k0 <= pl; k0 += AK) {
-        float sc[4][4] = {};
-        for (int d0 = 0; d0 < D; d0 += ADS) {
-            __syncthreads();
+        const int nk = min(AK, pl - k0 + 1);
+        size_t row_off[4];                               // this thread's 4 key rows of the tile, as (page, group, slot) bases
 #pragma unroll
-            for (int i = 0; i < AQ * ADS / 256; ++i) {
-                const int e = threadIdx.x + i * 256, r = e / ADS, kk = e % ADS, d = d0 + kk;
-                sq_[kk][r] = (r < rows && d < D) ? qh[(size_t)r * Hq * D + d] : 0.f;
-                const int pj = k0 + r;
-                float kv = 0.f;
-                if (pj <= pl && d < D)
-                    kv = ldf(k_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * D + d);
-                sk_[kk][r] = kv;
+        for (int j = 0; j < 4; ++j) {
+            const int pj = k0 + lr + 16 * j;
+            row_off[j] = pj <= pl ? ((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size : 0;
+        }
+        float sc[4][4] = {};
+        for (int d0 = 0; d0 < D; d0 += ADC) {
+            const int dn = min(ADC, D - d0);
+            __syncthreads();
+            if (!q_staged) {
+                for (int j = 0; j < 4; ++j) {
+                    const int r = lr + 16 * j;
+                    for (int d = lc; d < dn; d += 16) sq_[d * APQ + r] = r < rows ? qh[(size_t)r * Hq * D + d0 + d] : 0.f;
+                }
+                q_staged = q_once;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int r = lr + 16 * j;
+                const T* kr = k_pages + row_off[j] * D + d0;
+                if (r < nk) {
+#pragma unroll 8
+                    for (int d = lc; d < dn; d += 16) sk_[d * APQ + r] = kr[d];
+                } else {
+                    for (int d = lc; d < dn; d += 16) sk_[d * APQ + r] = T(0.f);
+                }
+            }
+            if (d0 == 0) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int r = lr + 16 * j;
+                    const T* vr = v_pages + row_off[j] * DV + c0;
+                    if (r < nk) {
+#pragma unroll 8
+                        for (int c = lc; c < AVW; c += 16) sv_[r * APV + c] = c0 + c < DV ? vr[c] : T(0.f);
+                    }
+                }
             }
             __syncthreads();
-#pragma unroll
-            for (int kk = 0; kk < ADS; ++kk) {
-                const float4 av = *reinterpret_cast<const float4*>(&sq_[kk][tm]);
-                const float4 bv = *reinterpret_cast<const float4*>(&sk_[kk][tn]);
-                const float a[4] = {av.x, av.y, av.z, av.w}, b[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll 8
+            for (int kk = 0; kk < dn; ++kk) {
+                const float4 av = *reinterpret_cast<const float4*>(sq_ + kk * APQ + tm);
+                const float a[4] = {av.x, av.y, av.z, av.w};
+                float b[4];
+                ld4(sk_ + kk * APQ + tn, b);
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -189,7 +243,7 @@ __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float*
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float pw = expf(sc[i][j] - mn);  // exp(-inf) = 0 for masked keys
-                sp_[tn + j][tm + i] = pw;
+                sp_[(tn + j) * APQ + tm + i] = pw;
                 rs += pw;
             }
 #pragma unroll
@@ -199,31 +253,21 @@ __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float*
 #pragma unroll
             for (int c = 0; c < 8; ++c) o[i][c] *= corr;
         }
-        for (int j0 = 0; j0 < AK; j0 += ADS) {
-            if (k0 + j0 > pl) break;                   // uniform over the CTA
-            __syncthreads();
+        __syncthreads();
+#pragma unroll 4
+        for (int kk = 0; kk < nk; ++kk) {
+            const float4 av = *reinterpret_cast<const float4*>(sp_ + kk * APQ + tm);
+            const float a[4] = {av.x, av.y, av.z, av.w};
+            float b0[4], b1[4];
+            ld4(sv_ + kk * APV + tn, b0);
+            ld4(sv_ + kk * APV + 64 + tn, b1);
 #pragma unroll
-            for (int i = 0; i < ADS * AVW / 256; ++i) {
-                const int e = threadIdx.x + i * 256, kk = e / AVW, c = e % AVW;
-                const int pj = k0 + j0 + kk;
-                float vv = 0.f;
-                if (pj <= pl && c0 + c < DV)
-                    vv = ldf(v_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * DV + c0 + c);
-                sv_[kk][c] = vv;
-            }
-            __syncthreads();
+            for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int kk = 0; kk < ADS; ++kk) {
-                const float4 av = *reinterpret_cast<const float4*>(&sp_[j0 + kk][tm]);
-                const float4 b0 = *reinterpret_cast<const float4*>(&sv_[kk][tn]);
-                const float4 b1 = *reinterpret_cast<const float4*>(&sv_[kk][64 + tn]);
-                const float a[4] = {av.x, av.y, av.z, av.w};
-                const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) o[i][c] = fmaf(a[i], b[c], o[i][c]);
-            }
+                for (int c = 0; c < 4; ++c) {
+                    o[i][c] = fmaf(a[i], b0[c], o[i][c]);
+                    o[i][4 + c] = fmaf(a[i], b1[c], o[i][4 + c]);
+                }
         }
     }
 #pragma unroll
@@ -239,6 +283,21 @@ __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float*
             if (col < DV) stf(out + (size_t)t * ld_out + (size_t)h * DV + col, o[i][c] * f);
         }
     }
+}
+
+template <typename T>
+int launch_attn_tiled(const float* q, const void* k_pages, const void* v_pages, const int* page_table, int page_size,
+                      const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D, int DV, int chunk,
+                      float scale, SeqPos pos, cudaStream_t s) {
+    static SmemAttrOnce once;
+    const size_t smem = attn_tiled_smem<T>(ADC);
+    if (ensure_dyn_smem(once, attn_chunk_sink_tiled_kernel<T>, (int)smem)) return -100;
+    dim3 grid((S + AQ - 1) / AQ, Hq, (DV + AVW - 1) / AVW);
+    count_launch();
+    attn_chunk_sink_tiled_kernel<T><<<grid, 256, attn_tiled_smem<T>(D), s>>>(q, (const T*)k_pages, (const T*)v_pages, page_table, page_size,
+                                                                            (const T*)gate, ld_gate, (T*)out, ld_out, S, Hq, G, D, DV,
+                                                                            chunk, scale, pos);
+    return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 
 }  // namespace
@@ -265,17 +324,11 @@ int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_p
     if (!q || !k_pages || !v_pages || !page_table || !out || S < 1 || Hq < 1 || G < 1 || Hq % G || D < 1 || DV < 1)
         return -2;
     if (S >= kAttnTiledMin) {
-        dim3 grid((S + AQ - 1) / AQ, Hq, (DV + AVW - 1) / AVW);
-        count_launch();
         if (dt == DT_F32)
-            attn_chunk_sink_tiled_kernel<float><<<grid, 256, 0, s>>>(q, (const float*)k_pages, (const float*)v_pages, page_table,
-                                                                     page_size, (const float*)gate, ld_gate, (float*)out, ld_out,
-                                                                     S, Hq, G, D, DV, chunk, scale, pos);
-        else
-            attn_chunk_sink_tiled_kernel<bf16><<<grid, 256, 0, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table,
-                                                                    page_size, (const bf16*)gate, ld_gate, (bf16*)out, ld_out, S,
-                                                                    Hq, G, D, DV, chunk, scale, pos);
-        return cudaGetLastError() == cudaSuccess ? 0 : -100;
+            return launch_attn_tiled<float>(q, k_pages, v_pages, page_table, page_size, gate, ld_gate, out, ld_out, S, Hq, G, D, DV,
+                                            chunk, scale, pos, s);
+        return launch_attn_tiled<bf16>(q, k_pages, v_pages, page_table, page_size, gate, ld_gate, out, ld_out, S, Hq, G, D, DV, chunk,
+                                       scale, pos, s);
     }
     // shared memory holds one score per key of the longest window a row of this call can have
     int max_keys = chunk;

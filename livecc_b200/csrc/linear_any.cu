@@ -63,23 +63,24 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(const T* __restrict__ 
     }
 }
 
-// Few rows (M <= 8): one warp per output column streams that row of W once with 16-byte loads (scalar loads when K or a
-// row start is not 16-byte aligned); lanes stride over k, each lane keeps one accumulator per row of A.
+// Few rows (M <= 8), the shape of a decode step: the weight matrix is streamed once (HBM-bound). A warp owns WR = 2
+// output columns and keeps WR x WU = 8 independent 16-byte non-allocating loads of their weight rows in flight per lane
+// before it touches the activations (which stay in L1); lanes stride over k and keep one accumulator per (column, row of
+// A). Scalar loads when K or a row start is not 16-byte aligned.
 constexpr int kRowsMax = 8;
+constexpr int WR = 2, WU = 4;
 template <typename T> struct Vec16;
 template <> struct Vec16<bf16> {
     static constexpr int N = 8;
-    static __device__ __forceinline__ void load(const bf16* p, float (&v)[8]) {
-        const uint4 u = *reinterpret_cast<const uint4*>(p);
+    static __device__ __forceinline__ void unpack(const uint4& u, float (&v)[8]) {
         const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
         v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
     }
 };
 template <> struct Vec16<float> {
     static constexpr int N = 4;
-    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
-        const float4 u = *reinterpret_cast<const float4*>(p);
-        v[0] = u.x; v[1] = u.y; v[2] = u.z; v[3] = u.w;
+    static __device__ __forceinline__ void unpack(const uint4& u, float (&v)[4]) {
+        v[0] = __uint_as_float(u.x); v[1] = __uint_as_float(u.y); v[2] = __uint_as_float(u.z); v[3] = __uint_as_float(u.w);
     }
 };
 
@@ -88,41 +89,66 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ 
                                                           const float* __restrict__ bias, TC* __restrict__ C, int ldc, int M,
                                                           int N, int K) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * 8 + warp;
-    if (n >= N) return;
-    const T* w = W + (size_t)n * ldw;
-    float acc[kRowsMax];
+    const int n0 = (blockIdx.x * 8 + warp) * WR;
+    if (n0 >= N) return;
+    float acc[WR][kRowsMax];
 #pragma unroll
-    for (int m = 0; m < kRowsMax; ++m) acc[m] = 0.f;
+    for (int r = 0; r < WR; ++r)
+#pragma unroll
+        for (int m = 0; m < kRowsMax; ++m) acc[r][m] = 0.f;
     if (VEC) {
         constexpr int V = Vec16<T>::N;
-#pragma unroll 2
-        for (int k = lane * V; k < K; k += 32 * V) {
-            float wv[V];
-            Vec16<T>::load(w + k, wv);
+        const T* w[WR];
 #pragma unroll
-            for (int m = 0; m < kRowsMax; ++m) {
-                if (m < M) {
-                    float av[V];
-                    Vec16<T>::load(A + (size_t)m * lda + k, av);
+        for (int r = 0; r < WR; ++r) w[r] = W + (size_t)min(n0 + r, N - 1) * ldw;
+        for (int kb = lane * V; kb < K; kb += 32 * V * WU) {
+            uint4 wq[WR][WU];
 #pragma unroll
-                    for (int i = 0; i < V; ++i) acc[m] = fmaf(av[i], wv[i], acc[m]);
+            for (int r = 0; r < WR; ++r)
+#pragma unroll
+                for (int u = 0; u < WU; ++u) {
+                    const int k = kb + u * 32 * V;
+                    wq[r][u] = k < K ? ld_stream16(w[r] + k) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+            for (int u = 0; u < WU; ++u) {
+                const int k = min(kb + u * 32 * V, K - V);      // past the end the weights are zero; keep the address valid
+                float wv[WR][V];
+#pragma unroll
+                for (int r = 0; r < WR; ++r) Vec16<T>::unpack(wq[r][u], wv[r]);
+#pragma unroll
+                for (int m = 0; m < kRowsMax; ++m) {
+                    if (m < M) {
+                        float av[V];
+                        Vec16<T>::unpack(__ldg(reinterpret_cast<const uint4*>(A + (size_t)m * lda + k)), av);
+#pragma unroll
+                        for (int r = 0; r < WR; ++r)
+#pragma unroll
+                            for (int i = 0; i < V; ++i) acc[r][m] = fmaf(av[i], wv[r][i], acc[r][m]);
+                    }
                 }
             }
         }
     } else {
         for (int k = lane; k < K; k += 32) {
-            const float wv = ldf(w + k);
 #pragma unroll
-            for (int m = 0; m < kRowsMax; ++m)
-                if (m < M) acc[m] = fmaf(ldf(A + (size_t)m * lda + k), wv, acc[m]);
+            for (int r = 0; r < WR; ++r) {
+                const float wv = ldf(W + (size_t)min(n0 + r, N - 1) * ldw + k);
+#pragma unroll
+                for (int m = 0; m < kRowsMax; ++m)
+                    if (m < M) acc[r][m] = fmaf(ldf(A + (size_t)m * lda + k), wv, acc[r][m]);
+            }
         }
     }
 #pragma unroll
-    for (int m = 0; m < kRowsMax; ++m) {
-        if (m < M) {
-            const float v = warp_sum(acc[m]);
-            if (lane == 0) stf(C + (size_t)m * ldc + n, v + (bias ? bias[n] : 0.f));
+    for (int r = 0; r < WR; ++r) {
+        const int n = n0 + r;
+#pragma unroll
+        for (int m = 0; m < kRowsMax; ++m) {
+            if (m < M) {
+                const float v = warp_sum(acc[r][m]);
+                if (lane == 0 && n < N) stf(C + (size_t)m * ldc + n, v + (bias ? bias[n] : 0.f));
+            }
         }
     }
 }
@@ -135,9 +161,9 @@ int launch_linear(const void* A, int lda, const void* W, int ldw, const float* b
         const bool vec = (K % V) == 0 && (lda % V) == 0 && (ldw % V) == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0;
         count_launch();
         if (vec)
-            linear_rows_kernel<T, TC, true><<<(N + 7) / 8, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K);
+            linear_rows_kernel<T, TC, true><<<(N + 8 * WR - 1) / (8 * WR), 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K);
         else
-            linear_rows_kernel<T, TC, false><<<(N + 7) / 8, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K);
+            linear_rows_kernel<T, TC, false><<<(N + 8 * WR - 1) / (8 * WR), 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K);
     } else {
         dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
         count_launch();

@@ -28,22 +28,38 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); 
 // ---- causal convolution -----------------------------------------------------------------------------------------------
 constexpr int kMaxTaps = 8;
 
-// out[t, c] = silu(b[c] + sum_j w[c, j] * in[t - (taps-1) + j, c]); rows before 0 come from the carry.
+// out[t, c] = silu(b[c] + sum_j w[c, j] * in[t - (taps-1) + j, c]); rows before 0 come from the carry. A thread owns one
+// channel over kConvRows consecutive rows and slides the window through registers, so every input is read once.
+constexpr int kConvRows = 8;
 template <typename T>
 __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int ld_in, T* __restrict__ out, int ld_out,
                                         const float* __restrict__ w, const float* __restrict__ b,
                                         const float* __restrict__ carry, int S, int C, int taps, SeqPos pos) {
     if (seq_done(pos)) return;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    const int t = blockIdx.y;
+    const int t0 = blockIdx.y * kConvRows;
     if (c >= C) return;
-    float acc = b[c];
-    for (int j = 0; j < taps; ++j) {
-        const int tt = t - (taps - 1) + j;
-        const float v = tt >= 0 ? ldf(in + (size_t)tt * ld_in + c) : carry[(size_t)c * (taps - 1) + (taps - 1 + tt)];
-        acc = fmaf(w[(size_t)c * taps + j], v, acc);
+    float wv[kMaxTaps], x[kMaxTaps + kConvRows - 1];
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j) wv[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+    // x[i] = input at row t0 - (taps-1) + i
+#pragma unroll
+    for (int i = 0; i < kMaxTaps + kConvRows - 1; ++i) {
+        const int tt = t0 - (taps - 1) + i;
+        float v = 0.f;
+        if (i < taps - 1 + kConvRows && tt < S) v = tt >= 0 ? ldf(in + (size_t)tt * ld_in + c) : carry[(size_t)c * (taps - 1) + (taps - 1 + tt)];
+        x[i] = v;
     }
-    stf(out + (size_t)t * ld_out + c, silu_f(acc));
+    const float bias = b[c];
+#pragma unroll
+    for (int r = 0; r < kConvRows; ++r) {
+        if (t0 + r >= S) break;
+        float acc = bias;
+#pragma unroll
+        for (int j = 0; j < kMaxTaps; ++j)
+            if (j < taps) acc = fmaf(wv[j], x[r + j], acc);
+        stf(out + (size_t)(t0 + r) * ld_out + c, silu_f(acc));
+    }
 }
 
 // carry[c, i] <- input at row S - (taps-1) + i (an older carry entry when that row is negative)
@@ -174,7 +190,7 @@ __global__ void __launch_bounds__(kScanThreads) gated_scan_kernel(ScanArgs a, Se
 int causal_conv_silu(int dt, const void* in, int ld_in, void* out, int ld_out, const float* w, const float* b,
                      float* carry, int S, int C, int taps, SeqPos pos, cudaStream_t s) {
     if (!in || !out || !w || !b || !carry || S < 1 || C < 1 || taps < 1 || taps > kMaxTaps) return -2;
-    dim3 grid((C + 127) / 128, S);
+    dim3 grid((C + 127) / 128, (S + kConvRows - 1) / kConvRows);
     count_launch();
     if (dt == DT_F32)
         causal_conv_silu_kernel<float><<<grid, 128, 0, s>>>((const float*)in, ld_in, (float*)out, ld_out, w, b, carry, S, C, taps, pos);

@@ -83,10 +83,19 @@ __global__ void chunk_cumsum_kernel(ChunkArgs a, SeqPos pos) {
     if (seq_done(pos)) return;
     const int col = blockIdx.y * blockDim.x + threadIdx.x, ncol = a.heads * a.NV;
     if (col >= ncol) return;
-    const int t0 = blockIdx.x * CL, t1 = min(t0 + CL, a.S);
+    const int t0 = blockIdx.x * CL, len = min(CL, a.S - t0);
     float* p = a.la + (size_t)(a.row0 + t0) * ncol + col;
     float acc = 0.f;
-    for (int t = t0; t < t1; ++t, p += ncol) { acc += *p; *p = acc; }
+    for (int tb = 0; tb < len; tb += 16) {     // 16 independent loads in flight, then the running sum in row order
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = tb + i < len ? p[(size_t)(tb + i) * ncol] : 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            acc += v[i];
+            if (tb + i < len) p[(size_t)(tb + i) * ncol] = acc;
+        }
+    }
 }
 
 // ---- 2: M[t, s] -------------------------------------------------------------------------------------------------------
@@ -94,7 +103,11 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) chunk_weights_kernel(ChunkArgs a, SeqPos pos) {
     if (seq_done(pos)) return;
     __shared__ float sc_[KS][PAD], sk_[KS][PAD], sb_[KS][PAD];
-    const int blk = blockIdx.x, h = blockIdx.y, g = h / a.heads_per_group;
+    // a decay per head: the product c k^T is the same for every head of a group, so a CTA forms it once per group and
+    // writes one decayed copy per head; a decay per key channel: one CTA per head
+    const int blk = blockIdx.x, g = VEC ? blockIdx.y / a.heads_per_group : blockIdx.y;
+    const int h_first = VEC ? blockIdx.y : g * a.heads_per_group, h_count = VEC ? 1 : a.heads_per_group;
+    const int h = h_first;
     const int t0 = blk * CL, len = min(CL, a.S - t0);
     const int N = a.N, ncol = a.heads * a.NV;
     const int ty = threadIdx.x / 16, tx = threadIdx.x % 16, tm = ty * 4, tn = tx * 4;
@@ -133,19 +146,22 @@ __global__ void __launch_bounds__(256) chunk_weights_kernel(ChunkArgs a, SeqPos 
                 }
         }
     }
-    float* out = a.ws_m + ((size_t)blk * a.heads + h) * CL * CL;
+    for (int hh = h_first; hh < h_first + h_count; ++hh) {
+        float* out = a.ws_m + ((size_t)blk * a.heads + hh) * CL * CL;
+        const float* hb = a.la + (size_t)(a.row0 + t0) * ncol + (size_t)hh * a.NV;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int t = tm + i;
+        for (int i = 0; i < 4; ++i) {
+            const int t = tm + i;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int s = tn + j;
-            float v = 0.f;
-            if (s <= t && t < len) {
-                v = acc[i][j] * a.cs * (a.sc ? a.sc[(size_t)(a.row0 + t0 + s) * a.heads + h] : 1.f);
-                if (!VEC) v *= expf(fminf(gb[(size_t)t * ncol] - gb[(size_t)s * ncol], 0.f));
+            for (int j = 0; j < 4; ++j) {
+                const int s = tn + j;
+                float v = 0.f;
+                if (s <= t && t < len) {
+                    v = acc[i][j] * a.cs * (a.sc ? a.sc[(size_t)(a.row0 + t0 + s) * a.heads + hh] : 1.f);
+                    if (!VEC) v *= expf(fminf(hb[(size_t)t * ncol] - hb[(size_t)s * ncol], 0.f));
+                }
+                out[t * CL + s] = v;
             }
-            out[t * CL + s] = v;
         }
     }
 }
@@ -165,16 +181,26 @@ __global__ void __launch_bounds__(256) chunk_state_kernel(ChunkArgs a, SeqPos po
     const float* gsc = a.sc ? a.sc + (size_t)(a.row0 + t0) * a.heads + h : nullptr;
     const float* blast = gb + (size_t)(len - 1) * ncol;
     const int tm = (threadIdx.x / 16) * 4, tn = (threadIdx.x % 16) * 4;
+    __shared__ float rowf[CL];     // per row: the step scale, and in the per-head case the decay from the row to the block's end
+    if (threadIdx.x < CL) {
+        const int s = threadIdx.x;
+        float f = 0.f;
+        if (s < len) {
+            f = gsc ? gsc[(size_t)s * a.heads] : 1.f;
+            if (!VEC) f *= expf(fminf(blast[0] - gb[(size_t)s * ncol], 0.f));
+        }
+        rowf[s] = f;
+    }
     float acc[4][4] = {};
     for (int s0 = 0; s0 < len; s0 += KS) {
         __syncthreads();
         stage<false, false>(sh,
             [&](int r, int kk) { const int s = s0 + kk, p = p0 + r;
-                                 return (s < len && p < P) ? ldf(gu + (size_t)s * a.ld_u + p) * (gsc ? gsc[(size_t)s * a.heads] : 1.f) : 0.f; },
+                                 return (s < len && p < P) ? ldf(gu + (size_t)s * a.ld_u + p) * rowf[s] : 0.f; },
             [&](int r, int kk) { const int s = s0 + kk, n = n0 + r;
                                  if (s >= len || n >= N) return 0.f;
-                                 const float d = VEC ? blast[n] - gb[(size_t)s * ncol + n] : blast[0] - gb[(size_t)s * ncol];
-                                 return ldf(gk + (size_t)s * a.ld_k + n) * expf(fminf(d, 0.f)); });
+                                 const float kv = ldf(gk + (size_t)s * a.ld_k + n);
+                                 return VEC ? kv * expf(fminf(blast[n] - gb[(size_t)s * ncol + n], 0.f)) : kv; });
         __syncthreads();
         fma_slice(sh, tm, tn, acc);
     }
@@ -201,12 +227,25 @@ __global__ void chunk_prefix_kernel(ChunkArgs a, int nblocks, SeqPos pos) {
     const int n = (int)(idx % a.N), h = (int)(idx / ((size_t)a.P * a.N));
     const int ncol = a.heads * a.NV;
     float st = a.state[idx];
-    for (int b = 0; b < nblocks; ++b) {
-        const int tlast = min((b + 1) * CL, a.S) - 1;
-        const float d = a.ws_s[(size_t)b * per + idx];
-        const float lb = a.la[(size_t)(a.row0 + tlast) * ncol + (size_t)h * a.NV + (VEC ? n : 0)];
-        a.ws_s[(size_t)b * per + idx] = st;
-        st = fmaf(expf(lb), st, d);
+    for (int b0 = 0; b0 < nblocks; b0 += 8) {  // 8 blocks' loads in flight together; the chain over blocks runs in registers
+        float d[8], e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int b = b0 + i;
+            if (b < nblocks) {
+                const int tlast = min((b + 1) * CL, a.S) - 1;
+                d[i] = a.ws_s[(size_t)b * per + idx];
+                e[i] = a.la[(size_t)(a.row0 + tlast) * ncol + (size_t)h * a.NV + (VEC ? n : 0)];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int b = b0 + i;
+            if (b < nblocks) {
+                a.ws_s[(size_t)b * per + idx] = st;
+                st = fmaf(expf(e[i]), st, d[i]);
+            }
+        }
     }
     a.state[idx] = st;
 }
@@ -278,7 +317,7 @@ int run_chunked(const ScanArgs& s, SeqPos pos, cudaStream_t st) {
         count_launch();
         chunk_cumsum_kernel<<<dim3(nb, (ncol + 127) / 128), 128, 0, st>>>(a, pos);
         count_launch();
-        chunk_weights_kernel<T, VEC><<<dim3(nb, s.heads), 256, 0, st>>>(a, pos);
+        chunk_weights_kernel<T, VEC><<<dim3(nb, VEC ? s.heads : s.heads / s.heads_per_group), 256, 0, st>>>(a, pos);
         count_launch();
         chunk_state_kernel<T, VEC><<<dim3(nb * s.heads, (s.P + TS - 1) / TS, (s.N + TS - 1) / TS), 256, 0, st>>>(a, pos);
         count_launch();

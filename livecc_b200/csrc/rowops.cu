@@ -78,25 +78,27 @@ __global__ void __launch_bounds__(256) postnorm_residual_kernel(float* __restric
     }
 }
 
-// One warp per (row, group).
-template <typename T>
+// A team of TEAM threads (a warp, or a whole CTA for wide groups) per (row, group).
+template <typename T, int TEAM>
 __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __restrict__ y, int ld_y, const T* __restrict__ gate,
                                                                int ld_gate, const float* __restrict__ w, int w_len, T* __restrict__ out,
                                                                int ld_out, int S, int n, int group, int gate_first, float eps) {
+    __shared__ float red[32];
     const int ngroups = n / group;
-    const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const int wid = TEAM == 32 ? blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5) : blockIdx.x;
+    const int lane = TEAM == 32 ? (threadIdx.x & 31) : threadIdx.x;
     if (wid >= S * ngroups) return;
     const int r = wid / ngroups, c0 = (wid % ngroups) * group;
     const float* yr = y + (size_t)r * ld_y + c0;
     const T* gr = gate + (size_t)r * ld_gate + c0;
     float ss = 0.f;
-    for (int c = lane; c < group; c += 32) {
+    for (int c = lane; c < group; c += TEAM) {
         const float v = gate_first ? yr[c] * silu_f(ldf(gr + c)) : yr[c];
         ss = fmaf(v, v, ss);
     }
-    ss = warp_sum(ss);
+    ss = TEAM == 32 ? warp_sum(ss) : block_sum(ss, red);
     const float rn = 1.f / sqrtf(ss / (float)group + eps);
-    for (int c = lane; c < group; c += 32) {
+    for (int c = lane; c < group; c += TEAM) {
         const float gsl = silu_f(ldf(gr + c));
         const float wv = w[(c0 + c) % w_len];
         const float v = gate_first ? yr[c] * gsl * rn * wv : yr[c] * rn * wv * gsl;
@@ -161,12 +163,18 @@ int postnorm_residual(int dt, float* x32, void* xa, const void* a, int ld_a, con
 int gated_group_norm(int dt, const float* y, int ld_y, const void* gate, int ld_gate, const float* w, int w_len,
                      void* out, int ld_out, int S, int n, int group, int gate_first, float eps, cudaStream_t s) {
     if (!y || !gate || !w || !out || S < 1 || n < 1 || group < 1 || n % group || w_len < 1) return -2;
-    const int warps = S * (n / group);
+    const int teams = S * (n / group);
     count_launch();
-    if (dt == DT_F32)
-        gated_group_norm_kernel<float><<<(warps + 7) / 8, 256, 0, s>>>(y, ld_y, (const float*)gate, ld_gate, w, w_len, (float*)out, ld_out, S, n, group, gate_first, eps);
-    else
-        gated_group_norm_kernel<bf16><<<(warps + 7) / 8, 256, 0, s>>>(y, ld_y, (const bf16*)gate, ld_gate, w, w_len, (bf16*)out, ld_out, S, n, group, gate_first, eps);
+    // the team size depends on the group's width alone, so a row is summed in the same order in every batch and portion
+#define LCC_GGN(T, TEAM, GRID)                                                                                                   \
+    gated_group_norm_kernel<T, TEAM><<<GRID, 256, 0, s>>>(y, ld_y, (const T*)gate, ld_gate, w, w_len, (T*)out, ld_out, S, n, group, \
+                                                          gate_first, eps)
+    if (group >= 256) {
+        if (dt == DT_F32) LCC_GGN(float, 256, teams); else LCC_GGN(bf16, 256, teams);
+    } else {
+        if (dt == DT_F32) LCC_GGN(float, 32, (teams + 7) / 8); else LCC_GGN(bf16, 32, (teams + 7) / 8);
+    }
+#undef LCC_GGN
     return done();
 }
 
