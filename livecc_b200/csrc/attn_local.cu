@@ -7,6 +7,7 @@
 
 #include "common.cuh"
 #include "launch.h"
+#include "mma.cuh"
 #include "seqmix.h"
 
 namespace lcc {
@@ -300,6 +301,218 @@ int launch_attn_tiled(const float* q, const void* k_pages, const void* v_pages, 
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 
+// bf16 storage, head sizes up to 256: the same tiling on the tensor cores. One CTA of 4 warps per (64 query rows, query
+// head, 128 output channels); a warp owns 16 query rows. Q (rounded to bf16 once), the K tile and the V tile sit in shared
+// memory as bf16 rows padded to whole 16-channel steps (zeros; when rows are 16-byte aligned the K/V tiles are double-
+// buffered asynchronous copies); scores and the product with V are mma.sync m16n8k16 with
+// fp32 accumulators, the softmax (running max and sum started at the sink's term, exp in fp32) works on the accumulator
+// fragments, and the weights go to the second product as bf16 A fragments straight from registers.
+constexpr int MQ = 64, MK = 64, MVW = 128, MLV = MVW + 8;
+
+// rows that are not 16-byte aligned: element-wise staging
+template <typename RowPtr>
+__device__ __forceinline__ void stage_bf16_rows(bf16* dst, int ld_dst, int ncp, int ncv, RowPtr rowptr) {
+    for (int u = threadIdx.x; u < MK * ncp; u += blockDim.x) {
+        const int r = u / ncp, c = u % ncp;
+        const bf16* p = rowptr(r);
+        dst[(size_t)r * ld_dst + c] = (p && c < ncv) ? p[c] : __float2bfloat16_rn(0.f);
+    }
+}
+
+template <bool VEC8>
+__global__ void __launch_bounds__(128) attn_chunk_sink_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pages,
+                                                                  const bf16* __restrict__ v_pages, const int* __restrict__ page_table,
+                                                                  int page_size, const bf16* __restrict__ gate, int ld_gate,
+                                                                  bf16* __restrict__ out, int ld_out, int S, int Hq, int G, int D, int DV,
+                                                                  int chunk, float scale, SeqPos pos) {
+    if (seq_done(pos)) return;
+    extern __shared__ __align__(16) uint8_t smem_attn[];
+    const int Dp = (D + 15) / 16 * 16, LQ = Dp + 8;
+    bf16* sQ = reinterpret_cast<bf16*>(smem_attn);     // [MQ][LQ]
+    bf16* sK0 = sQ + (size_t)MQ * LQ;                   // [2][MK][LQ]   (the second buffer only with VEC8)
+    bf16* sV0 = sK0 + (size_t)(VEC8 ? 2 : 1) * MK * LQ; // [2][MK][MLV]
+    const int t0 = (gridDim.x - 1 - blockIdx.x) * MQ, h = blockIdx.y, c0 = blockIdx.z * MVW;
+    const int g = h / (Hq / G);
+    const int past = seq_past(pos, S);
+    const int rows = min(MQ, S - t0);
+    const int pf = past + t0, pl = pf + rows - 1;
+    const int kbeg = chunk > 0 ? (pf / chunk) * chunk : 0;
+    const int dvv = min(MVW, DV - c0), DVp = (dvv + 15) / 16 * 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+    // queries: fp32 -> bf16, zero padding
+    for (int u = threadIdx.x; u < MQ * (Dp / 2); u += blockDim.x) {
+        const int r = u / (Dp / 2), d = (u % (Dp / 2)) * 2;
+        const float* qr = q + ((size_t)(t0 + r) * Hq + h) * D;
+        const float v0 = (r < rows && d < D) ? qr[d] : 0.f, v1 = (r < rows && d + 1 < D) ? qr[d + 1] : 0.f;
+        *reinterpret_cast<uint32_t*>(sQ + (size_t)r * LQ + d) = pack_bf16x2(v0, v1);
+    }
+    const int r_lo = warp * 16 + gq;                    // this thread's two rows of the tile: r_lo and r_lo + 8
+    int p_row[2], lo_row[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        p_row[i] = pf + r_lo + 8 * i;
+        lo_row[i] = chunk > 0 ? (p_row[i] / chunk) * chunk : 0;
+    }
+    float m[2] = {0.f, 0.f};
+    float l[2] = {tq == 0 ? 1.f : 0.f, tq == 0 ? 1.f : 0.f};     // per-thread partial sums; the sink's 1 is counted once per row
+    float o[16][4] = {};
+    // VEC8: a tile's K and V rows arrive by 16-byte asynchronous copies (zero-filled past the last key and in the padding
+    // columns), all in flight together, into the buffer the previous tile does not use, while that tile is computed
+    auto issue = [&](int k0, int buf) {
+        bf16* dK = sK0 + (size_t)buf * MK * LQ;
+        bf16* dV = sV0 + (size_t)buf * MK * MLV;
+        const int kpr = Dp / 8, vpr = DVp / 8;
+        for (int u = threadIdx.x; u < MK * (kpr + vpr); u += blockDim.x) {
+            const int r = u / (kpr + vpr), cu = u % (kpr + vpr);
+            const int pj = k0 + r;
+            const bool row_ok = pj <= pl;
+            const size_t ro = row_ok ? ((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size : 0;
+            if (cu < kpr) {
+                const int c = cu * 8;
+                const bool ok = row_ok && c < D;
+                cp_async16(dK + (size_t)r * LQ + c, ok ? k_pages + ro * D + c : k_pages, ok);
+            } else {
+                const int c = (cu - kpr) * 8;
+                const bool ok = row_ok && c < dvv;
+                cp_async16(dV + (size_t)r * MLV + c, ok ? v_pages + ro * DV + c0 + c : v_pages, ok);
+            }
+        }
+        cp_async_commit();
+    };
+    if (VEC8) issue(kbeg, 0);
+    int it = 0;
+    for (int k0 = kbeg; k0 <= pl; k0 += MK, ++it) {
+        const int buf = VEC8 ? (it & 1) : 0;
+        const bf16* sK = sK0 + (size_t)buf * MK * LQ;
+        const bf16* sV = sV0 + (size_t)buf * MK * MLV;
+        if (VEC8) {
+            cp_async_wait<0>();
+            __syncthreads();       // this tile has landed for every thread, and every thread is done with the other buffer
+            if (k0 + MK <= pl) issue(k0 + MK, buf ^ 1);
+        } else {
+            auto krow = [&](int r) -> const bf16* {
+                const int pj = k0 + r;
+                return pj <= pl ? k_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * D : nullptr;
+            };
+            auto vrow = [&](int r) -> const bf16* {
+                const int pj = k0 + r;
+                return pj <= pl ? v_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * DV + c0 : nullptr;
+            };
+            __syncthreads();
+            stage_bf16_rows(sK0, LQ, Dp, D, krow);
+            stage_bf16_rows(sV0, MLV, DVp, dvv, vrow);
+            __syncthreads();
+        }
+        float sc[8][4] = {};
+        for (int ks = 0; ks < Dp; ks += 16) {
+            uint32_t a[4];
+            ldmatrix_x4(a[0], a[1], a[2], a[3], sQ + (size_t)(warp * 16 + (lane & 15)) * LQ + ks + (lane >> 4) * 8);
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(b0, b1, b2, b3, sK + (size_t)(np * 16 + (lane & 7) + (lane >> 4) * 8) * LQ + ks + ((lane >> 3) & 1) * 8);
+                mma_bf16_16816(sc[2 * np], a, b0, b1);
+                mma_bf16_16816(sc[2 * np + 1], a, b2, b3);
+            }
+        }
+        // softmax on the fragments: elements 0, 1 belong to row r_lo, elements 2, 3 to row r_lo + 8; columns j * 8 + 2 tq (+1)
+        float corr[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int pj = k0 + j * 8 + 2 * tq + e;
+                    const bool ok = pj <= p_row[i] && pj >= lo_row[i] && r_lo + 8 * i < rows;
+                    const float v = ok ? sc[j][2 * i + e] * scale : -INFINITY;
+                    sc[j][2 * i + e] = v;
+                    mx = fmaxf(mx, v);
+                }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float mn = fmaxf(m[i], mx);          // finite: m starts at the sink's score
+            corr[i] = expf(m[i] - mn);
+            float rs = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float pw = expf(sc[j][2 * i + e] - mn);
+                    sc[j][2 * i + e] = pw;
+                    rs += pw;
+                }
+            l[i] = fmaf(l[i], corr[i], rs);
+            m[i] = mn;
+        }
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt) { o[nt][0] *= corr[0]; o[nt][1] *= corr[0]; o[nt][2] *= corr[1]; o[nt][3] *= corr[1]; }
+#pragma unroll
+        for (int j2 = 0; j2 < 4; ++j2) {
+            if (k0 + j2 * 16 > pl) break;              // uniform: the tile's remaining keys do not exist
+            uint32_t a[4];
+            a[0] = pack_bf16x2(sc[2 * j2][0], sc[2 * j2][1]);
+            a[1] = pack_bf16x2(sc[2 * j2][2], sc[2 * j2][3]);
+            a[2] = pack_bf16x2(sc[2 * j2 + 1][0], sc[2 * j2 + 1][1]);
+            a[3] = pack_bf16x2(sc[2 * j2 + 1][2], sc[2 * j2 + 1][3]);
+#pragma unroll
+            for (int ntp = 0; ntp < 8; ++ntp) {
+                if (ntp * 16 < DVp) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(b0, b1, b2, b3, sV + (size_t)(j2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * MLV + ntp * 16 + (lane >> 4) * 8);
+                    mma_bf16_16816(o[2 * ntp], a, b0, b1);
+                    mma_bf16_16816(o[2 * ntp + 1], a, b2, b3);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float lt = l[i];
+        lt += __shfl_xor_sync(0xffffffffu, lt, 1);
+        lt += __shfl_xor_sync(0xffffffffu, lt, 2);
+        const int r = r_lo + 8 * i, t = t0 + r;
+        if (r >= rows) continue;
+        float gv = 1.f;
+        if (gate) gv = 1.f / (1.f + expf(-ldf(gate + (size_t)t * ld_gate + h)));
+        const float f = gv / lt;
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int col = nt * 8 + 2 * tq + e;
+                if (col < dvv) stf(out + (size_t)t * ld_out + (size_t)h * DV + c0 + col, o[nt][2 * i + e] * f);
+            }
+    }
+}
+
+int launch_attn_mma(const float* q, const void* k_pages, const void* v_pages, const int* page_table, int page_size,
+                    const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D, int DV, int chunk,
+                    float scale, SeqPos pos, cudaStream_t s) {
+    static SmemAttrOnce once8, once1;
+    const int Dp = (D + 15) / 16 * 16;
+    // 16-byte copies need every K and V row (and the output-channel slice) to start on a 16-byte boundary
+    const bool vec8 = (D % 8) == 0 && (DV % 8) == 0 && ((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0;
+    const int nbuf = vec8 ? 2 : 1;
+    const size_t smem = ((size_t)MQ * (Dp + 8) + (size_t)nbuf * MK * (Dp + 8 + MLV)) * sizeof(bf16);
+    const size_t smem_max = ((size_t)MQ * (kAttnMmaMaxDim + 8) + (size_t)nbuf * MK * (kAttnMmaMaxDim + 8 + MLV)) * sizeof(bf16);
+    dim3 grid((S + MQ - 1) / MQ, Hq, (DV + MVW - 1) / MVW);
+    count_launch();
+    if (vec8) {
+        if (ensure_dyn_smem(once8, attn_chunk_sink_mma_kernel<true>, (int)smem_max)) return -100;
+        attn_chunk_sink_mma_kernel<true><<<grid, 128, smem, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table, page_size,
+                                                                 (const bf16*)gate, ld_gate, (bf16*)out, ld_out, S, Hq, G, D, DV, chunk,
+                                                                 scale, pos);
+    } else {
+        if (ensure_dyn_smem(once1, attn_chunk_sink_mma_kernel<false>, (int)smem_max)) return -100;
+        attn_chunk_sink_mma_kernel<false><<<grid, 128, smem, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table, page_size,
+                                                                  (const bf16*)gate, ld_gate, (bf16*)out, ld_out, S, Hq, G, D, DV, chunk,
+                                                                  scale, pos);
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
 }  // namespace
 
 int qk_norm_kv_append(int dt, const void* proj, int ld, const float* qn_w, const float* kn_w, float eps, float* q_out,
@@ -320,10 +533,13 @@ int qk_norm_kv_append(int dt, const void* proj, int ld, const float* qn_w, const
 
 int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_pages, const int* page_table,
                     int page_size, const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D,
-                    int DV, int chunk, float scale, SeqPos pos, cudaStream_t s) {
+                    int DV, int chunk, float scale, bool tensor_cores, SeqPos pos, cudaStream_t s) {
     if (!q || !k_pages || !v_pages || !page_table || !out || S < 1 || Hq < 1 || G < 1 || Hq % G || D < 1 || DV < 1)
         return -2;
     if (S >= kAttnTiledMin) {
+        if (dt == DT_BF16 && tensor_cores && D <= kAttnMmaMaxDim)
+            return launch_attn_mma(q, k_pages, v_pages, page_table, page_size, gate, ld_gate, out, ld_out, S, Hq, G, D, DV, chunk,
+                                   scale, pos, s);
         if (dt == DT_F32)
             return launch_attn_tiled<float>(q, k_pages, v_pages, page_table, page_size, gate, ld_gate, out, ld_out, S, Hq, G, D, DV,
                                             chunk, scale, pos, s);

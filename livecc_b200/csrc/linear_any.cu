@@ -63,12 +63,13 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(const T* __restrict__ 
     }
 }
 
-// Few rows (M <= 8), the shape of a decode step: the weight matrix is streamed once (HBM-bound). A warp owns WR = 2
-// output columns and keeps WR x WU = 8 independent 16-byte non-allocating loads of their weight rows in flight per lane
-// before it touches the activations (which stay in L1); lanes stride over k and keep one accumulator per (column, row of
-// A). Scalar loads when K or a row start is not 16-byte aligned.
+// Few rows (M <= 8), the shape of a decode step: the weight matrix is streamed once (HBM-bound). A warp owns WR output
+// columns (2 for wide matrices; 1, in CTAs of 2 warps, when N is small, so that every SM still has enough loads in
+// flight) and keeps WR x WU independent 16-byte non-allocating loads of their weight rows in flight per lane before it
+// touches the activations (which stay in L1); lanes stride over k and keep one accumulator per (column, row of A), so
+// the order of a column's sum does not depend on WR or M. Scalar loads when K or a row start is not 16-byte aligned.
 constexpr int kRowsMax = 8;
-constexpr int WR = 2, WU = 4;
+constexpr int WU = 4;
 template <typename T> struct Vec16;
 template <> struct Vec16<bf16> {
     static constexpr int N = 8;
@@ -84,12 +85,12 @@ template <> struct Vec16<float> {
     }
 };
 
-template <typename T, typename TC, bool VEC>
+template <typename T, typename TC, bool VEC, int WR>
 __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int ldw,
                                                           const float* __restrict__ bias, TC* __restrict__ C, int ldc, int M,
                                                           int N, int K) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = (blockIdx.x * 8 + warp) * WR;
+    const int n0 = (blockIdx.x * (blockDim.x >> 5) + warp) * WR;
     if (n0 >= N) return;
     float acc[WR][kRowsMax];
 #pragma unroll
@@ -160,10 +161,15 @@ int launch_linear(const void* A, int lda, const void* W, int ldw, const float* b
         constexpr int V = Vec16<T>::N;
         const bool vec = (K % V) == 0 && (lda % V) == 0 && (ldw % V) == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0;
         count_launch();
-        if (vec)
-            linear_rows_kernel<T, TC, true><<<(N + 8 * WR - 1) / (8 * WR), 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K);
-        else
-            linear_rows_kernel<T, TC, false><<<(N + 8 * WR - 1) / (8 * WR), 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K);
+#define LCC_ROWS(VECB, WRN, WARPS)                                                                                         \
+    linear_rows_kernel<T, TC, VECB, WRN><<<(N + WARPS * WRN - 1) / (WARPS * WRN), WARPS * 32, 0, s>>>((const T*)A, lda, (const T*)W, \
+                                                                                                      ldw, bias, (TC*)C, ldc, M, N, K)
+        if (N >= 8192) {
+            if (vec) LCC_ROWS(true, 2, 8); else LCC_ROWS(false, 2, 8);
+        } else {
+            if (vec) LCC_ROWS(true, 1, 2); else LCC_ROWS(false, 1, 2);
+        }
+#undef LCC_ROWS
     } else {
         dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
         count_launch();

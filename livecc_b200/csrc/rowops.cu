@@ -38,8 +38,10 @@ __global__ void embed_sinusoid_kernel(const int64_t* __restrict__ ids, const int
     }
 }
 
-// One CTA per row; three passes over the row (the operands stay in L1/L2).
-template <typename T>
+// One CTA per row. Rows of up to 256 * kRowCache elements are read once into registers (every load in flight together);
+// wider rows are re-read from L1/L2 in each of the three passes. Both forms add in the same order.
+constexpr int kRowCache = 16;
+template <typename T, bool CACHE>
 __global__ void __launch_bounds__(256) postnorm_residual_kernel(float* __restrict__ x32, T* __restrict__ xa, const T* __restrict__ a,
                                                                 int ld_a, const float* __restrict__ wa, const T* __restrict__ b,
                                                                 int ld_b, const float* __restrict__ wb, const float* __restrict__ w,
@@ -49,13 +51,28 @@ __global__ void __launch_bounds__(256) postnorm_residual_kernel(float* __restric
     float* x = x32 + (size_t)r * W;
     const T* ar = a + (size_t)r * ld_a;
     const T* br = b ? b + (size_t)r * ld_b : nullptr;
+    float va[kRowCache], vb[kRowCache], vx[kRowCache];
+    if (CACHE) {
+#pragma unroll
+        for (int i = 0; i < kRowCache; ++i) {
+            const int c = threadIdx.x + i * 256;
+            va[i] = c < W ? ldf(ar + c) : 0.f;
+            vb[i] = (br && c < W) ? ldf(br + c) : 0.f;
+            vx[i] = c < W ? x[c] : 0.f;
+        }
+    }
     float ra = 1.f, rb = 1.f;
     if (br) {
         float sa = 0.f, sb = 0.f;
-        for (int c = threadIdx.x; c < W; c += blockDim.x) {
-            const float va = ldf(ar + c), vb = ldf(br + c);
-            sa = fmaf(va, va, sa);
-            sb = fmaf(vb, vb, sb);
+        if (CACHE) {
+#pragma unroll
+            for (int i = 0; i < kRowCache; ++i) { sa = fmaf(va[i], va[i], sa); sb = fmaf(vb[i], vb[i], sb); }
+        } else {
+            for (int c = threadIdx.x; c < W; c += blockDim.x) {
+                const float ta = ldf(ar + c), tb = ldf(br + c);
+                sa = fmaf(ta, ta, sa);
+                sb = fmaf(tb, tb, sb);
+            }
         }
         sa = block_sum(sa, red);
         sb = block_sum(sb, red);
@@ -63,23 +80,48 @@ __global__ void __launch_bounds__(256) postnorm_residual_kernel(float* __restric
         rb = 1.f / sqrtf(sb / (float)W + eps);
     }
     float ss = 0.f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float m = br ? 0.5f * (ldf(ar + c) * ra * wa[c] + ldf(br + c) * rb * wb[c]) : ldf(ar + c);
-        const float v = fmaf(alpha, x[c], m);
-        ss = fmaf(v, v, ss);
+    if (CACHE) {
+#pragma unroll
+        for (int i = 0; i < kRowCache; ++i) {
+            const int c = threadIdx.x + i * 256;
+            if (c < W) {
+                const float m = br ? 0.5f * (va[i] * ra * wa[c] + vb[i] * rb * wb[c]) : va[i];
+                vx[i] = fmaf(alpha, vx[i], m);
+                ss = fmaf(vx[i], vx[i], ss);
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < W; c += blockDim.x) {
+            const float m = br ? 0.5f * (ldf(ar + c) * ra * wa[c] + ldf(br + c) * rb * wb[c]) : ldf(ar + c);
+            const float v = fmaf(alpha, x[c], m);
+            ss = fmaf(v, v, ss);
+        }
     }
     ss = block_sum(ss, red);
     const float rn = 1.f / sqrtf(ss / (float)W + eps);
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float m = br ? 0.5f * (ldf(ar + c) * ra * wa[c] + ldf(br + c) * rb * wb[c]) : ldf(ar + c);
-        const float v = fmaf(alpha, x[c], m) * rn * w[c];
-        x[c] = v;
-        stf(xa + (size_t)r * W + c, v);
+    if (CACHE) {
+#pragma unroll
+        for (int i = 0; i < kRowCache; ++i) {
+            const int c = threadIdx.x + i * 256;
+            if (c < W) {
+                const float v = vx[i] * rn * w[c];
+                x[c] = v;
+                stf(xa + (size_t)r * W + c, v);
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < W; c += blockDim.x) {
+            const float m = br ? 0.5f * (ldf(ar + c) * ra * wa[c] + ldf(br + c) * rb * wb[c]) : ldf(ar + c);
+            const float v = fmaf(alpha, x[c], m) * rn * w[c];
+            x[c] = v;
+            stf(xa + (size_t)r * W + c, v);
+        }
     }
 }
 
-// A team of TEAM threads (a warp, or a whole CTA for wide groups) per (row, group).
-template <typename T, int TEAM>
+// A team of TEAM threads (a warp, or a whole CTA for wide groups) per (row, group). Groups of up to TEAM * kRowCache
+// columns are read once into registers; wider ones are re-read in the second pass.
+template <typename T, int TEAM, bool CACHE>
 __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __restrict__ y, int ld_y, const T* __restrict__ gate,
                                                                int ld_gate, const float* __restrict__ w, int w_len, T* __restrict__ out,
                                                                int ld_out, int S, int n, int group, int gate_first, float eps) {
@@ -91,18 +133,45 @@ __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __re
     const int r = wid / ngroups, c0 = (wid % ngroups) * group;
     const float* yr = y + (size_t)r * ld_y + c0;
     const T* gr = gate + (size_t)r * ld_gate + c0;
+    float vy[kRowCache], vg[kRowCache];
     float ss = 0.f;
-    for (int c = lane; c < group; c += TEAM) {
-        const float v = gate_first ? yr[c] * silu_f(ldf(gr + c)) : yr[c];
-        ss = fmaf(v, v, ss);
+    if (CACHE) {
+#pragma unroll
+        for (int i = 0; i < kRowCache; ++i) {
+            const int c = lane + i * TEAM;
+            vy[i] = c < group ? yr[c] : 0.f;
+            vg[i] = c < group ? ldf(gr + c) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < kRowCache; ++i) {
+            vg[i] = silu_f(vg[i]);
+            const float v = gate_first ? vy[i] * vg[i] : vy[i];
+            ss = fmaf(v, v, ss);
+        }
+    } else {
+        for (int c = lane; c < group; c += TEAM) {
+            const float v = gate_first ? yr[c] * silu_f(ldf(gr + c)) : yr[c];
+            ss = fmaf(v, v, ss);
+        }
     }
     ss = TEAM == 32 ? warp_sum(ss) : block_sum(ss, red);
     const float rn = 1.f / sqrtf(ss / (float)group + eps);
-    for (int c = lane; c < group; c += TEAM) {
-        const float gsl = silu_f(ldf(gr + c));
-        const float wv = w[(c0 + c) % w_len];
-        const float v = gate_first ? yr[c] * gsl * rn * wv : yr[c] * rn * wv * gsl;
-        stf(out + (size_t)r * ld_out + c0 + c, v);
+    if (CACHE) {
+#pragma unroll
+        for (int i = 0; i < kRowCache; ++i) {
+            const int c = lane + i * TEAM;
+            if (c < group) {
+                const float wv = w[(c0 + c) % w_len];
+                stf(out + (size_t)r * ld_out + c0 + c, gate_first ? vy[i] * vg[i] * rn * wv : vy[i] * rn * wv * vg[i]);
+            }
+        }
+    } else {
+        for (int c = lane; c < group; c += TEAM) {
+            const float gsl = silu_f(ldf(gr + c));
+            const float wv = w[(c0 + c) % w_len];
+            const float v = gate_first ? yr[c] * gsl * rn * wv : yr[c] * rn * wv * gsl;
+            stf(out + (size_t)r * ld_out + c0 + c, v);
+        }
     }
 }
 
@@ -153,10 +222,14 @@ int postnorm_residual(int dt, float* x32, void* xa, const void* a, int ld_a, con
                       const float* wb, const float* w, float alpha, float eps, int S, int W, cudaStream_t s) {
     if (!x32 || !xa || !a || !w || S < 1 || W < 1 || (b && (!wa || !wb))) return -2;
     count_launch();
-    if (dt == DT_F32)
-        postnorm_residual_kernel<float><<<S, 256, 0, s>>>(x32, (float*)xa, (const float*)a, ld_a, wa, (const float*)b, ld_b, wb, w, alpha, eps, W);
-    else
-        postnorm_residual_kernel<bf16><<<S, 256, 0, s>>>(x32, (bf16*)xa, (const bf16*)a, ld_a, wa, (const bf16*)b, ld_b, wb, w, alpha, eps, W);
+#define LCC_PNR(T, CACHE) \
+    postnorm_residual_kernel<T, CACHE><<<S, 256, 0, s>>>(x32, (T*)xa, (const T*)a, ld_a, wa, (const T*)b, ld_b, wb, w, alpha, eps, W)
+    if (W <= 256 * kRowCache) {
+        if (dt == DT_F32) LCC_PNR(float, true); else LCC_PNR(bf16, true);
+    } else {
+        if (dt == DT_F32) LCC_PNR(float, false); else LCC_PNR(bf16, false);
+    }
+#undef LCC_PNR
     return done();
 }
 
@@ -166,13 +239,15 @@ int gated_group_norm(int dt, const float* y, int ld_y, const void* gate, int ld_
     const int teams = S * (n / group);
     count_launch();
     // the team size depends on the group's width alone, so a row is summed in the same order in every batch and portion
-#define LCC_GGN(T, TEAM, GRID)                                                                                                   \
-    gated_group_norm_kernel<T, TEAM><<<GRID, 256, 0, s>>>(y, ld_y, (const T*)gate, ld_gate, w, w_len, (T*)out, ld_out, S, n, group, \
-                                                          gate_first, eps)
-    if (group >= 256) {
-        if (dt == DT_F32) LCC_GGN(float, 256, teams); else LCC_GGN(bf16, 256, teams);
+#define LCC_GGN(T, TEAM, CACHE, GRID)                                                                                     \
+    gated_group_norm_kernel<T, TEAM, CACHE><<<GRID, 256, 0, s>>>(y, ld_y, (const T*)gate, ld_gate, w, w_len, (T*)out, ld_out, S, n, \
+                                                                 group, gate_first, eps)
+    if (group <= 32 * kRowCache) {
+        if (dt == DT_F32) LCC_GGN(float, 32, true, (teams + 7) / 8); else LCC_GGN(bf16, 32, true, (teams + 7) / 8);
+    } else if (group <= 256 * kRowCache) {
+        if (dt == DT_F32) LCC_GGN(float, 256, true, teams); else LCC_GGN(bf16, 256, true, teams);
     } else {
-        if (dt == DT_F32) LCC_GGN(float, 32, (teams + 7) / 8); else LCC_GGN(bf16, 32, (teams + 7) / 8);
+        if (dt == DT_F32) LCC_GGN(float, 256, false, teams); else LCC_GGN(bf16, 256, false, teams);
     }
 #undef LCC_GGN
     return done();

@@ -21,7 +21,7 @@ struct lcc_seq_model {
     uint8_t* ws = nullptr;
     size_t ws_bytes = 0;
     int cap_tokens = 0, cap_want = 0;
-    bool use_tc = true;  // bf16 linear layers with >= 64 rows and 8-aligned shapes go to the tcgen05 GEMM (LIVECC_B200_SEQ_TC=0: never)
+    bool use_tc = true;  // bf16: large 8-aligned linear layers go to the tcgen05 GEMM, prompt attention to the mma kernel (LIVECC_B200_SEQ_TC=0: never)
 };
 
 namespace {
@@ -278,7 +278,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                      "q/k norm + cache append");
                 STEP(lcc::attn_chunk_sink(dt, q, en.k_pages[li], en.v_pages[li], en.page_table, page_size,
                                           pr + (size_t)(z.l_nq + z.l_nk + z.l_nv) * es, ldl, mid + (size_t)r0 * ldo * es, ldo, en.n_new,
-                                          l.l_heads, l.l_kv_heads, l.l_dim, l.l_vdim, l.l_chunk, l.l_scale, pos, s), "chunk attention");
+                                          l.l_heads, l.l_kv_heads, l.l_dim, l.l_vdim, l.l_chunk, l.l_scale, m->use_tc, pos, s), "chunk attention");
                 r0 += en.n_new;
             }
             STEP(linear(m, mid, ldo, l.l_out, nullptr, o1, W, false, T, W, z.l_o, s), "attention out-proj");

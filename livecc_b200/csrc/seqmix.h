@@ -87,10 +87,14 @@ int qk_norm_kv_append(int dt, const void* proj, int ld, const float* qn_w, const
 // floor(j / chunk) == floor(i / chunk); weights exp(s_j) / (1 + sum_j exp(s_j)) (a sink with score 0 and no value);
 // head h's output is multiplied by sigmoid(gate[h]). q: fp32 [S, Hq*D]; gate: [S, Hq] slice (storage dt, leading dim
 // ld_gate) or null; out: [S, Hq*DV] (storage dt). chunk <= 0 means one chunk (plain causal attention).
-constexpr int kAttnTiledMin = 16;   // rows from which the tiled kernel runs (below: one CTA per row and head)
+// Three kernels: one CTA per (row, head) for decode steps and portions of fewer than kAttnTiledMin rows; a tiled fp32
+// CUDA-core kernel for longer portions; and, for bf16 storage with head size <= kAttnMmaMaxDim when tensor_cores is set,
+// the same tiling with both products on the tensor cores (bf16 operands, fp32 accumulation, fp32 softmax).
+constexpr int kAttnTiledMin = 16;
+constexpr int kAttnMmaMaxDim = 256;
 int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_pages, const int* page_table,
                     int page_size, const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D,
-                    int DV, int chunk, float scale, SeqPos pos, cudaStream_t s);
+                    int DV, int chunk, float scale, bool tensor_cores, SeqPos pos, cudaStream_t s);
 
 // ---- rowops.cu ----------------------------------------------------------------------------------------------------------
 // x[r, :] = table[id_r, :] * scale + sinusoid(past + r): entry 2i = sin(p * inv_freq[i]), 2i+1 = cos of the same.
