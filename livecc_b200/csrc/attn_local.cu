@@ -301,8 +301,9 @@ int launch_attn_tiled(const float* q, const void* k_pages, const void* v_pages, 
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 
-// bf16 storage, head sizes up to 256: the same tiling on the tensor cores. One CTA of 4 warps per (64 query rows, query
-// head, 128 output channels); a warp owns 16 query rows. Q (rounded to bf16 once), the K tile and the V tile sit in shared
+// bf16 storage, head sizes up to 256: the same tiling on the tensor cores. One CTA per (64 query rows, query head, 128
+// output channels) of one or (head size <= 128, aligned rows) two groups of 4 warps; a warp owns 16 query rows, the groups
+// take alternate key tiles and merge their (max, sum, output) at the end. Q (rounded to bf16 once), the K tile and the V tile sit in shared
 // memory as bf16 rows padded to whole 16-channel steps (zeros; when rows are 16-byte aligned the K/V tiles are double-
 // buffered asynchronous copies); scores and the product with V are mma.sync m16n8k16 with
 // fp32 accumulators, the softmax (running max and sum started at the sink's term, exp in fp32) works on the accumulator
@@ -319,8 +320,8 @@ __device__ __forceinline__ void stage_bf16_rows(bf16* dst, int ld_dst, int ncp, 
     }
 }
 
-template <bool VEC8>
-__global__ void __launch_bounds__(128) attn_chunk_sink_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pages,
+template <bool VEC8, int KH>
+__global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pages,
                                                                   const bf16* __restrict__ v_pages, const int* __restrict__ page_table,
                                                                   int page_size, const bf16* __restrict__ gate, int ld_gate,
                                                                   bf16* __restrict__ out, int ld_out, int S, int Hq, int G, int D, int DV,
@@ -329,8 +330,9 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_mma_kernel(const float* _
     extern __shared__ __align__(16) uint8_t smem_attn[];
     const int Dp = (D + 15) / 16 * 16, LQ = Dp + 8;
     bf16* sQ = reinterpret_cast<bf16*>(smem_attn);     // [MQ][LQ]
-    bf16* sK0 = sQ + (size_t)MQ * LQ;                   // [2][MK][LQ]   (the second buffer only with VEC8)
-    bf16* sV0 = sK0 + (size_t)(VEC8 ? 2 : 1) * MK * LQ; // [2][MK][MLV]
+    constexpr int KT = KH * MK;                         // keys per step of the CTA: one 64-key tile per group of 4 warps
+    bf16* sK0 = sQ + (size_t)MQ * LQ;                   // [2][KT][LQ]   (the second buffer only with VEC8)
+    bf16* sV0 = sK0 + (size_t)(VEC8 ? 2 : 1) * KT * LQ; // [2][KT][MLV]
     const int t0 = (gridDim.x - 1 - blockIdx.x) * MQ, h = blockIdx.y, c0 = blockIdx.z * MVW;
     const int g = h / (Hq / G);
     const int past = seq_past(pos, S);
@@ -338,7 +340,7 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_mma_kernel(const float* _
     const int pf = past + t0, pl = pf + rows - 1;
     const int kbeg = chunk > 0 ? (pf / chunk) * chunk : 0;
     const int dvv = min(MVW, DV - c0), DVp = (dvv + 15) / 16 * 16;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+    const int warp = (threadIdx.x >> 5) & 3, kh = threadIdx.x >> 7, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
     // queries: fp32 -> bf16, zero padding
     for (int u = threadIdx.x; u < MQ * (Dp / 2); u += blockDim.x) {
         const int r = u / (Dp / 2), d = (u % (Dp / 2)) * 2;
@@ -354,48 +356,54 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_mma_kernel(const float* _
         lo_row[i] = chunk > 0 ? (p_row[i] / chunk) * chunk : 0;
     }
     float m[2] = {0.f, 0.f};
-    float l[2] = {tq == 0 ? 1.f : 0.f, tq == 0 ? 1.f : 0.f};     // per-thread partial sums; the sink's 1 is counted once per row
+    // per-thread partial sums; the sink's 1 is counted once per row (by one thread of the first group of warps)
+    float l[2] = {(tq == 0 && kh == 0) ? 1.f : 0.f, (tq == 0 && kh == 0) ? 1.f : 0.f};
     float o[16][4] = {};
     // VEC8: a tile's K and V rows arrive by 16-byte asynchronous copies (zero-filled past the last key and in the padding
     // columns), all in flight together, into the buffer the previous tile does not use, while that tile is computed
     auto issue = [&](int k0, int buf) {
-        bf16* dK = sK0 + (size_t)buf * MK * LQ;
-        bf16* dV = sV0 + (size_t)buf * MK * MLV;
-        const int kpr = Dp / 8, vpr = DVp / 8;
-        for (int u = threadIdx.x; u < MK * (kpr + vpr); u += blockDim.x) {
-            const int r = u / (kpr + vpr), cu = u % (kpr + vpr);
-            const int pj = k0 + r;
+        bf16* dK = sK0 + (size_t)buf * KT * LQ;
+        bf16* dV = sV0 + (size_t)buf * KT * MLV;
+        // a warp walks rows, its lanes walk a row's 16-byte pieces; page and slot advance without divisions
+        const int kpr = Dp / 8, vpr = DVp / 8, nw = blockDim.x >> 5, wid = threadIdx.x >> 5;
+        int pj = k0 + wid, pg = pj / page_size, slot = pj - pg * page_size;
+        for (int r = wid; r < KT; r += nw) {
             const bool row_ok = pj <= pl;
-            const size_t ro = row_ok ? ((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size : 0;
-            if (cu < kpr) {
-                const int c = cu * 8;
-                const bool ok = row_ok && c < D;
-                cp_async16(dK + (size_t)r * LQ + c, ok ? k_pages + ro * D + c : k_pages, ok);
-            } else {
-                const int c = (cu - kpr) * 8;
-                const bool ok = row_ok && c < dvv;
-                cp_async16(dV + (size_t)r * MLV + c, ok ? v_pages + ro * DV + c0 + c : v_pages, ok);
+            const size_t ro = row_ok ? ((size_t)page_table[pg] * G + g) * page_size + slot : 0;
+            for (int cu = lane; cu < kpr + vpr; cu += 32) {
+                if (cu < kpr) {
+                    const int c = cu * 8;
+                    const bool ok = row_ok && c < D;
+                    cp_async16(dK + (size_t)r * LQ + c, ok ? k_pages + ro * D + c : k_pages, ok);
+                } else {
+                    const int c = (cu - kpr) * 8;
+                    const bool ok = row_ok && c < dvv;
+                    cp_async16(dV + (size_t)r * MLV + c, ok ? v_pages + ro * DV + c0 + c : v_pages, ok);
+                }
             }
+            pj += nw; slot += nw;
+            while (slot >= page_size) { slot -= page_size; ++pg; }
         }
         cp_async_commit();
     };
     if (VEC8) issue(kbeg, 0);
     int it = 0;
-    for (int k0 = kbeg; k0 <= pl; k0 += MK, ++it) {
+    for (int kc = kbeg; kc <= pl; kc += KT, ++it) {
         const int buf = VEC8 ? (it & 1) : 0;
-        const bf16* sK = sK0 + (size_t)buf * MK * LQ;
-        const bf16* sV = sV0 + (size_t)buf * MK * MLV;
+        const int k0 = kc + kh * MK;                    // this group of warps' tile of the step
+        const bf16* sK = sK0 + ((size_t)buf * KT + kh * MK) * LQ;
+        const bf16* sV = sV0 + ((size_t)buf * KT + kh * MK) * MLV;
         if (VEC8) {
             cp_async_wait<0>();
             __syncthreads();       // this tile has landed for every thread, and every thread is done with the other buffer
-            if (k0 + MK <= pl) issue(k0 + MK, buf ^ 1);
+            if (kc + KT <= pl) issue(kc + KT, buf ^ 1);
         } else {
             auto krow = [&](int r) -> const bf16* {
-                const int pj = k0 + r;
+                const int pj = kc + r;
                 return pj <= pl ? k_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * D : nullptr;
             };
             auto vrow = [&](int r) -> const bf16* {
-                const int pj = k0 + r;
+                const int pj = kc + r;
                 return pj <= pl ? v_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * DV + c0 : nullptr;
             };
             __syncthreads();
@@ -403,6 +411,7 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_mma_kernel(const float* _
             stage_bf16_rows(sV0, MLV, DVp, dvv, vrow);
             __syncthreads();
         }
+        if (k0 > pl) continue;                          // no tile left for this group in the last step (barriers are above)
         float sc[8][4] = {};
         for (int ks = 0; ks < Dp; ks += 16) {
             uint32_t a[4];
@@ -415,7 +424,11 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_mma_kernel(const float* _
                 mma_bf16_16816(sc[2 * np + 1], a, b2, b3);
             }
         }
-        // softmax on the fragments: elements 0, 1 belong to row r_lo, elements 2, 3 to row r_lo + 8; columns j * 8 + 2 tq (+1)
+        // softmax on the fragments: elements 0, 1 belong to row r_lo, elements 2, 3 to row r_lo + 8; columns j * 8 + 2 tq (+1).
+        // A tile every row of the CTA sees in full (at or after the last row's chunk start, wholly before the first row)
+        // skips the mask. The exponentials are exp2 of pre-scaled arguments: their error (2^-22) is far below the bf16
+        // rounding of the weights that follows.
+        const bool full = k0 + MK - 1 <= pf && rows == MQ && (chunk <= 0 || k0 >= (pl / chunk) * chunk);
         float corr[2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -424,22 +437,27 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_mma_kernel(const float* _
             for (int j = 0; j < 8; ++j)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    const int pj = k0 + j * 8 + 2 * tq + e;
-                    const bool ok = pj <= p_row[i] && pj >= lo_row[i] && r_lo + 8 * i < rows;
-                    const float v = ok ? sc[j][2 * i + e] * scale : -INFINITY;
+                    float v = sc[j][2 * i + e] * scale;
+                    if (!full) {
+                        const int pj = k0 + j * 8 + 2 * tq + e;
+                        const bool ok = pj <= p_row[i] && pj >= lo_row[i] && r_lo + 8 * i < rows;
+                        v = ok ? v : -INFINITY;
+                    }
                     sc[j][2 * i + e] = v;
                     mx = fmaxf(mx, v);
                 }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const float mn = fmaxf(m[i], mx);          // finite: m starts at the sink's score
-            corr[i] = expf(m[i] - mn);
+            constexpr float kLog2e = 1.4426950408889634f;
+            corr[i] = exp2f((m[i] - mn) * kLog2e);
+            const float mn2 = mn * kLog2e;
             float rs = 0.f;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    const float pw = expf(sc[j][2 * i + e] - mn);
+                    const float pw = exp2f(fmaf(sc[j][2 * i + e], kLog2e, -mn2));
                     sc[j][2 * i + e] = pw;
                     rs += pw;
                 }
@@ -467,6 +485,36 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_mma_kernel(const float* _
             }
         }
     }
+    if (KH > 1) {
+        // the second group hands its (max, partial sum, unnormalised output) to the first through the tile buffers (K and V
+        // buffers are contiguous; every asynchronous copy was waited for in the last step)
+        float* xch = reinterpret_cast<float*>(sK0);
+        const int tix = threadIdx.x & 127;
+        __syncthreads();                                // every warp is done with the K/V buffers
+        if (kh == 1) {
+#pragma unroll
+            for (int nt = 0; nt < 16; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) xch[(nt * 4 + e) * 128 + tix] = o[nt][e];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) { xch[(64 + i) * 128 + tix] = m[i]; xch[(66 + i) * 128 + tix] = l[i]; }
+        }
+        __syncthreads();
+        if (kh == 1) return;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float m1 = xch[(64 + i) * 128 + tix], l1 = xch[(66 + i) * 128 + tix];
+            const float mn = fmaxf(m[i], m1);
+            const float f0 = expf(m[i] - mn), f1 = expf(m1 - mn);
+            l[i] = l[i] * f0 + l1 * f1;
+            m[i] = mn;
+#pragma unroll
+            for (int nt = 0; nt < 16; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e)
+                    o[nt][2 * i + e] = o[nt][2 * i + e] * f0 + xch[(nt * 4 + 2 * i + e) * 128 + tix] * f1;
+        }
+    }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         float lt = l[i];
@@ -490,26 +538,29 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_mma_kernel(const float* _
 int launch_attn_mma(const float* q, const void* k_pages, const void* v_pages, const int* page_table, int page_size,
                     const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D, int DV, int chunk,
                     float scale, SeqPos pos, cudaStream_t s) {
-    static SmemAttrOnce once8, once1;
+    static SmemAttrOnce once82, once81, once1;
     const int Dp = (D + 15) / 16 * 16;
     // 16-byte copies need every K and V row (and the output-channel slice) to start on a 16-byte boundary
     const bool vec8 = (D % 8) == 0 && (DV % 8) == 0 && ((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0;
-    const int nbuf = vec8 ? 2 : 1;
-    const size_t smem = ((size_t)MQ * (Dp + 8) + (size_t)nbuf * MK * (Dp + 8 + MLV)) * sizeof(bf16);
-    const size_t smem_max = ((size_t)MQ * (kAttnMmaMaxDim + 8) + (size_t)nbuf * MK * (kAttnMmaMaxDim + 8 + MLV)) * sizeof(bf16);
+    // two groups of warps (two key tiles per step) when four tiles of K and V fit beside Q; the exchange area of the final
+    // merge (68 floats per thread of a group, 34 KB) lies over the K and V buffers, whose V part alone is 68 KB
+    const bool two = vec8 && Dp <= 128;
+    const int nbuf = vec8 ? 2 : 1, kh = two ? 2 : 1;
+    auto bytes = [&](int dp) { return ((size_t)MQ * (dp + 8) + (size_t)nbuf * kh * MK * (dp + 8 + MLV)) * sizeof(bf16); };
+    const size_t smem = bytes(Dp), smem_max = bytes(two ? 128 : kAttnMmaMaxDim);
     dim3 grid((S + MQ - 1) / MQ, Hq, (DV + MVW - 1) / MVW);
     count_launch();
-    if (vec8) {
-        if (ensure_dyn_smem(once8, attn_chunk_sink_mma_kernel<true>, (int)smem_max)) return -100;
-        attn_chunk_sink_mma_kernel<true><<<grid, 128, smem, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table, page_size,
-                                                                 (const bf16*)gate, ld_gate, (bf16*)out, ld_out, S, Hq, G, D, DV, chunk,
-                                                                 scale, pos);
-    } else {
-        if (ensure_dyn_smem(once1, attn_chunk_sink_mma_kernel<false>, (int)smem_max)) return -100;
-        attn_chunk_sink_mma_kernel<false><<<grid, 128, smem, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table, page_size,
-                                                                  (const bf16*)gate, ld_gate, (bf16*)out, ld_out, S, Hq, G, D, DV, chunk,
-                                                                  scale, pos);
-    }
+#define LCC_ATTN_MMA(ONCE, VEC, KHN)                                                                                         \
+    do {                                                                                                                     \
+        if (ensure_dyn_smem(ONCE, attn_chunk_sink_mma_kernel<VEC, KHN>, (int)smem_max)) return -100;                         \
+        attn_chunk_sink_mma_kernel<VEC, KHN><<<grid, 128 * KHN, smem, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table, \
+                                                                           page_size, (const bf16*)gate, ld_gate, (bf16*)out, ld_out, \
+                                                                           S, Hq, G, D, DV, chunk, scale, pos);              \
+    } while (0)
+    if (two) LCC_ATTN_MMA(once82, true, 2);
+    else if (vec8) LCC_ATTN_MMA(once81, true, 1);
+    else LCC_ATTN_MMA(once1, false, 1);
+#undef LCC_ATTN_MMA
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 

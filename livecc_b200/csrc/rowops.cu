@@ -242,7 +242,7 @@ int gated_group_norm(int dt, const float* y, int ld_y, const void* gate, int ld_
 #define LCC_GGN(T, TEAM, CACHE, GRID)                                                                                     \
     gated_group_norm_kernel<T, TEAM, CACHE><<<GRID, 256, 0, s>>>(y, ld_y, (const T*)gate, ld_gate, w, w_len, (T*)out, ld_out, S, n, \
                                                                  group, gate_first, eps)
-    if (group <= 32 * kRowCache) {
+    if (group <= 128) {
         if (dt == DT_F32) LCC_GGN(float, 32, true, (teams + 7) / 8); else LCC_GGN(bf16, 32, true, (teams + 7) / 8);
     } else if (group <= 256 * kRowCache) {
         if (dt == DT_F32) LCC_GGN(float, 256, true, teams); else LCC_GGN(bf16, 256, true, teams);

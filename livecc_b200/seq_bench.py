@@ -17,11 +17,11 @@ SIZES = {
     "w2048": (2048, 8, 5632, 1024),
     "w4096": (4096, 4, 11008, 1024),
 }
-PATTERN = ("mamba2", "mamba2", "parallel", "mamba2", "mamba2")
+PATTERN = ("mamba2", "mamba2", "mamba2", "parallel")
 
 
 def seq_config(width: int, n_layers: int, ff: int, chunk: int, vocab: int = 32768) -> SeqModelConfig:
-    """State-space layers with 2x expansion (64-channel heads, 128 states), every third-ish layer a parallel layer with
+    """State-space layers with 2x expansion (64-channel heads, 128 states), every fourth layer a parallel layer with
     128-wide attention heads (8 query heads per key/value head) beside gated linear attention, feed-forward on the
     parallel layers."""
     layers = []
@@ -34,10 +34,10 @@ def seq_config(width: int, n_layers: int, ff: int, chunk: int, vocab: int = 3276
             layers.append({"type": "parallel", "mlp": {"ff": ff, "kind": "dense"},
                            "mixer": {"left": dict(heads=heads, kv_heads=max(1, heads // 8), dim=128, vdim=128, mask={"size": chunk},
                                                   scale=128 ** -0.5),
-                                     "right": dict(heads=width // 256, dim=128, vdim=256, tau=16.0)}})
+                                     "right": dict(heads=width // 256, dim=128, vdim=256, tau=8.0)}})
     return SeqModelConfig.from_json({"architecture": "Bimopel", "vocab": vocab, "width": width, "layers": layers,
                                      "norm": {"eps": 1e-5}, "postln_alpha": 2.0, "embedding": {"scale": width ** 0.5},
-                                     "logit_softcap": 30.0})
+                                     "logit_softcap": 50.0})
 
 
 def qwen_config(width: int, n_layers: int, ff: int, vocab: int = 32768) -> LiveCCConfig:

@@ -199,15 +199,17 @@ def test_strong_and_weak_decays_in_the_block_form():
     _check_long(d, tensors, 200, [70, 137], seed=51, tol=2 * F32_TOL)
 
 
-def test_heads_wider_than_one_tile():
-    """Key, value and state sizes above 64 and 128 (several tiles per head, ragged last tiles), one chunk that is longer
-    than a key tile and one that is shorter, a long chunk whose last key tile ends on the row itself."""
-    layers = [seq_cases.par(heads=2, kv_heads=1, dim=72, vdim=136, chunk=150, scale=0.2, r_heads=1, r_dim=70, r_vdim=67, tau=8.0, ff=None),
+@pytest.mark.parametrize("dim,vdim", [(72, 136), (136, 72)])
+def test_heads_wider_than_one_tile(dim, vdim):
+    """Key, value and state sizes above 64 and 128 (several tiles per head, ragged last tiles), a chunk that is longer than
+    two key tiles, a last key tile that ends on the row itself. Head size 72 runs the attention's two-group form, 136 the
+    one-group form."""
+    layers = [seq_cases.par(heads=2, kv_heads=1, dim=dim, vdim=vdim, chunk=150, scale=0.2, r_heads=1, r_dim=70, r_vdim=67, tau=8.0, ff=None),
               seq_cases.ssd(heads=2, vdim=66, state=68, groups=1, conv=3, norm_groups=2)]
     d = seq_cases.config(layers, width=32, vocab=64)
     tensors = synthetic_seq_tensors(SeqModelConfig.from_json(d), seed=14)
     _check_long(d, tensors, 215, [64, 128, 129, 193], seed=52)
-    # the same sizes in bf16 storage: the tensor-core attention pads 72 channels to 80 and cuts 136 outputs into 128 + 8
+    # the same sizes in bf16 storage: the tensor-core attention pads 72 channels to 80 (136 to 144) and cuts 136 outputs into 128 + 8
     from livecc_b200.seq_engine import SeqLMForCausalLM
 
     toks = seq_cases.tokens(215, d["vocab"], seed=52)
