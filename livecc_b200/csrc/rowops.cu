@@ -38,10 +38,10 @@ __global__ void embed_sinusoid_kernel(const int64_t* __restrict__ ids, const int
     }
 }
 
-// One CTA per row. Rows of up to 256 * kRowCache elements are read once into registers (every load in flight together);
-// wider rows are re-read from L1/L2 in each of the three passes. Both forms add in the same order.
+// One CTA per row. Rows of up to 256 * kRowCache elements are read once into registers (E per thread, every load in flight
+// together); wider rows (E = 0) are re-read from L1/L2 in each of the three passes. Every form adds in the same order.
 constexpr int kRowCache = 16;
-template <typename T, bool CACHE>
+template <typename T, int E>
 __global__ void __launch_bounds__(256) postnorm_residual_kernel(float* __restrict__ x32, T* __restrict__ xa, const T* __restrict__ a,
                                                                 int ld_a, const float* __restrict__ wa, const T* __restrict__ b,
                                                                 int ld_b, const float* __restrict__ wb, const float* __restrict__ w,
@@ -51,10 +51,12 @@ __global__ void __launch_bounds__(256) postnorm_residual_kernel(float* __restric
     float* x = x32 + (size_t)r * W;
     const T* ar = a + (size_t)r * ld_a;
     const T* br = b ? b + (size_t)r * ld_b : nullptr;
-    float va[kRowCache], vb[kRowCache], vx[kRowCache];
+    constexpr bool CACHE = E > 0;
+    constexpr int EN = E > 0 ? E : 1;
+    float va[EN], vb[EN], vx[EN];
     if (CACHE) {
 #pragma unroll
-        for (int i = 0; i < kRowCache; ++i) {
+        for (int i = 0; i < EN; ++i) {
             const int c = threadIdx.x + i * 256;
             va[i] = c < W ? ldf(ar + c) : 0.f;
             vb[i] = (br && c < W) ? ldf(br + c) : 0.f;
@@ -66,7 +68,7 @@ __global__ void __launch_bounds__(256) postnorm_residual_kernel(float* __restric
         float sa = 0.f, sb = 0.f;
         if (CACHE) {
 #pragma unroll
-            for (int i = 0; i < kRowCache; ++i) { sa = fmaf(va[i], va[i], sa); sb = fmaf(vb[i], vb[i], sb); }
+            for (int i = 0; i < EN; ++i) { sa = fmaf(va[i], va[i], sa); sb = fmaf(vb[i], vb[i], sb); }
         } else {
             for (int c = threadIdx.x; c < W; c += blockDim.x) {
                 const float ta = ldf(ar + c), tb = ldf(br + c);
@@ -82,7 +84,7 @@ __global__ void __launch_bounds__(256) postnorm_residual_kernel(float* __restric
     float ss = 0.f;
     if (CACHE) {
 #pragma unroll
-        for (int i = 0; i < kRowCache; ++i) {
+        for (int i = 0; i < EN; ++i) {
             const int c = threadIdx.x + i * 256;
             if (c < W) {
                 const float m = br ? 0.5f * (va[i] * ra * wa[c] + vb[i] * rb * wb[c]) : va[i];
@@ -101,7 +103,7 @@ __global__ void __launch_bounds__(256) postnorm_residual_kernel(float* __restric
     const float rn = 1.f / sqrtf(ss / (float)W + eps);
     if (CACHE) {
 #pragma unroll
-        for (int i = 0; i < kRowCache; ++i) {
+        for (int i = 0; i < EN; ++i) {
             const int c = threadIdx.x + i * 256;
             if (c < W) {
                 const float v = vx[i] * rn * w[c];
@@ -119,9 +121,9 @@ __global__ void __launch_bounds__(256) postnorm_residual_kernel(float* __restric
     }
 }
 
-// A team of TEAM threads (a warp, or a whole CTA for wide groups) per (row, group). Groups of up to TEAM * kRowCache
-// columns are read once into registers; wider ones are re-read in the second pass.
-template <typename T, int TEAM, bool CACHE>
+// A team of TEAM threads (a warp, or a whole CTA for groups wider than 128 columns) per (row, group). Groups of up to
+// TEAM * kRowCache columns are read once into registers (E per thread); wider ones (E = 0) are re-read in the second pass.
+template <typename T, int TEAM, int E>
 __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __restrict__ y, int ld_y, const T* __restrict__ gate,
                                                                int ld_gate, const float* __restrict__ w, int w_len, T* __restrict__ out,
                                                                int ld_out, int S, int n, int group, int gate_first, float eps) {
@@ -131,19 +133,22 @@ __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __re
     const int lane = TEAM == 32 ? (threadIdx.x & 31) : threadIdx.x;
     if (wid >= S * ngroups) return;
     const int r = wid / ngroups, c0 = (wid % ngroups) * group;
+    const int wb = c0 % w_len;                 // weight index of the group's first column (one division per team)
     const float* yr = y + (size_t)r * ld_y + c0;
     const T* gr = gate + (size_t)r * ld_gate + c0;
-    float vy[kRowCache], vg[kRowCache];
+    constexpr bool CACHE = E > 0;
+    constexpr int EN = E > 0 ? E : 1;
+    float vy[EN], vg[EN];
     float ss = 0.f;
     if (CACHE) {
 #pragma unroll
-        for (int i = 0; i < kRowCache; ++i) {
+        for (int i = 0; i < EN; ++i) {
             const int c = lane + i * TEAM;
             vy[i] = c < group ? yr[c] : 0.f;
             vg[i] = c < group ? ldf(gr + c) : 0.f;
         }
 #pragma unroll
-        for (int i = 0; i < kRowCache; ++i) {
+        for (int i = 0; i < EN; ++i) {
             vg[i] = silu_f(vg[i]);
             const float v = gate_first ? vy[i] * vg[i] : vy[i];
             ss = fmaf(v, v, ss);
@@ -158,17 +163,19 @@ __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __re
     const float rn = 1.f / sqrtf(ss / (float)group + eps);
     if (CACHE) {
 #pragma unroll
-        for (int i = 0; i < kRowCache; ++i) {
+        for (int i = 0; i < EN; ++i) {
             const int c = lane + i * TEAM;
             if (c < group) {
-                const float wv = w[(c0 + c) % w_len];
+                const int wi = wb + c;
+                const float wv = w[wi < w_len ? wi : wi % w_len];
                 stf(out + (size_t)r * ld_out + c0 + c, gate_first ? vy[i] * vg[i] * rn * wv : vy[i] * rn * wv * vg[i]);
             }
         }
     } else {
         for (int c = lane; c < group; c += TEAM) {
             const float gsl = silu_f(ldf(gr + c));
-            const float wv = w[(c0 + c) % w_len];
+            const int wi = wb + c;
+            const float wv = w[wi < w_len ? wi : wi % w_len];
             const float v = gate_first ? yr[c] * gsl * rn * wv : yr[c] * rn * wv * gsl;
             stf(out + (size_t)r * ld_out + c0 + c, v);
         }
@@ -222,13 +229,19 @@ int postnorm_residual(int dt, float* x32, void* xa, const void* a, int ld_a, con
                       const float* wb, const float* w, float alpha, float eps, int S, int W, cudaStream_t s) {
     if (!x32 || !xa || !a || !w || S < 1 || W < 1 || (b && (!wa || !wb))) return -2;
     count_launch();
-#define LCC_PNR(T, CACHE) \
-    postnorm_residual_kernel<T, CACHE><<<S, 256, 0, s>>>(x32, (T*)xa, (const T*)a, ld_a, wa, (const T*)b, ld_b, wb, w, alpha, eps, W)
-    if (W <= 256 * kRowCache) {
-        if (dt == DT_F32) LCC_PNR(float, true); else LCC_PNR(bf16, true);
-    } else {
-        if (dt == DT_F32) LCC_PNR(float, false); else LCC_PNR(bf16, false);
-    }
+#define LCC_PNR(E)                                                                                                          \
+    do {                                                                                                                    \
+        if (dt == DT_F32)                                                                                                   \
+            postnorm_residual_kernel<float, E><<<S, 256, 0, s>>>(x32, (float*)xa, (const float*)a, ld_a, wa, (const float*)b, ld_b, wb, w, alpha, eps, W); \
+        else                                                                                                                \
+            postnorm_residual_kernel<bf16, E><<<S, 256, 0, s>>>(x32, (bf16*)xa, (const bf16*)a, ld_a, wa, (const bf16*)b, ld_b, wb, w, alpha, eps, W); \
+    } while (0)
+    const int per = (W + 255) / 256;
+    if (per <= 2) LCC_PNR(2);
+    else if (per <= 4) LCC_PNR(4);
+    else if (per <= 8) LCC_PNR(8);
+    else if (per <= kRowCache) LCC_PNR(16);
+    else LCC_PNR(0);
 #undef LCC_PNR
     return done();
 }
@@ -239,15 +252,25 @@ int gated_group_norm(int dt, const float* y, int ld_y, const void* gate, int ld_
     const int teams = S * (n / group);
     count_launch();
     // the team size depends on the group's width alone, so a row is summed in the same order in every batch and portion
-#define LCC_GGN(T, TEAM, CACHE, GRID)                                                                                     \
-    gated_group_norm_kernel<T, TEAM, CACHE><<<GRID, 256, 0, s>>>(y, ld_y, (const T*)gate, ld_gate, w, w_len, (T*)out, ld_out, S, n, \
-                                                                 group, gate_first, eps)
+#define LCC_GGN(TEAM, E, GRID)                                                                                            \
+    do {                                                                                                                  \
+        if (dt == DT_F32)                                                                                                 \
+            gated_group_norm_kernel<float, TEAM, E><<<GRID, 256, 0, s>>>(y, ld_y, (const float*)gate, ld_gate, w, w_len, (float*)out, \
+                                                                         ld_out, S, n, group, gate_first, eps);           \
+        else                                                                                                              \
+            gated_group_norm_kernel<bf16, TEAM, E><<<GRID, 256, 0, s>>>(y, ld_y, (const bf16*)gate, ld_gate, w, w_len, (bf16*)out,    \
+                                                                        ld_out, S, n, group, gate_first, eps);            \
+    } while (0)
     if (group <= 128) {
-        if (dt == DT_F32) LCC_GGN(float, 32, true, (teams + 7) / 8); else LCC_GGN(bf16, 32, true, (teams + 7) / 8);
-    } else if (group <= 256 * kRowCache) {
-        if (dt == DT_F32) LCC_GGN(float, 256, true, teams); else LCC_GGN(bf16, 256, true, teams);
+        LCC_GGN(32, 4, (teams + 7) / 8);
     } else {
-        if (dt == DT_F32) LCC_GGN(float, 256, false, teams); else LCC_GGN(bf16, 256, false, teams);
+        const int per = (group + 255) / 256;
+        if (per <= 1) LCC_GGN(256, 1, teams);
+        else if (per <= 2) LCC_GGN(256, 2, teams);
+        else if (per <= 4) LCC_GGN(256, 4, teams);
+        else if (per <= 8) LCC_GGN(256, 8, teams);
+        else if (per <= kRowCache) LCC_GGN(256, 16, teams);
+        else LCC_GGN(256, 0, teams);
     }
 #undef LCC_GGN
     return done();
