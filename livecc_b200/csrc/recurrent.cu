@@ -29,12 +29,14 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); 
 constexpr int kMaxTaps = 8;
 
 // out[t, c] = silu(b[c] + sum_j w[c, j] * in[t - (taps-1) + j, c]); rows before 0 come from the carry. A thread owns one
-// channel over kConvRows consecutive rows and slides the window through registers, so every input is read once.
+// channel over kConvRows consecutive rows and slides the window through registers, so every input is read once. When the
+// call has no more than kConvRows rows (a decode step), the same thread also writes the channel's new carry (carry_out),
+// which it alone reads and writes; longer calls update the carry in a second launch, after every block has read it.
 constexpr int kConvRows = 8;
 template <typename T>
 __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int ld_in, T* __restrict__ out, int ld_out,
                                         const float* __restrict__ w, const float* __restrict__ b,
-                                        const float* __restrict__ carry, int S, int C, int taps, SeqPos pos) {
+                                        const float* carry, float* carry_out, int S, int C, int taps, SeqPos pos) {
     if (seq_done(pos)) return;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int t0 = blockIdx.y * kConvRows;
@@ -53,12 +55,20 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int ld_in, T* 
     const float bias = b[c];
 #pragma unroll
     for (int r = 0; r < kConvRows; ++r) {
-        if (t0 + r >= S) break;
         float acc = bias;
 #pragma unroll
         for (int j = 0; j < kMaxTaps; ++j)
             if (j < taps) acc = fmaf(wv[j], x[r + j], acc);
-        stf(out + (size_t)(t0 + r) * ld_out + c, silu_f(acc));
+        if (t0 + r < S) stf(out + (size_t)(t0 + r) * ld_out + c, silu_f(acc));
+    }
+    if (carry_out) {
+        // new carry[i] = input at row S - (taps-1) + i; an older carry entry when that row is negative: entry S + i, which lies
+        // above every entry written so far (i ascending), so the update can run in place
+        const int n = taps - 1;
+        for (int i = 0; i < n; ++i) {
+            const int tt = S - n + i;
+            carry_out[(size_t)c * n + i] = tt >= 0 ? ldf(in + (size_t)tt * ld_in + c) : carry[(size_t)c * n + (n + tt)];
+        }
     }
 }
 
@@ -191,12 +201,14 @@ int causal_conv_silu(int dt, const void* in, int ld_in, void* out, int ld_out, c
                      float* carry, int S, int C, int taps, SeqPos pos, cudaStream_t s) {
     if (!in || !out || !w || !b || !carry || S < 1 || C < 1 || taps < 1 || taps > kMaxTaps) return -2;
     dim3 grid((C + 127) / 128, (S + kConvRows - 1) / kConvRows);
+    const bool fused = taps > 1 && S <= kConvRows;
+    float* carry_out = fused ? carry : nullptr;
     count_launch();
     if (dt == DT_F32)
-        causal_conv_silu_kernel<float><<<grid, 128, 0, s>>>((const float*)in, ld_in, (float*)out, ld_out, w, b, carry, S, C, taps, pos);
+        causal_conv_silu_kernel<float><<<grid, 128, 0, s>>>((const float*)in, ld_in, (float*)out, ld_out, w, b, carry, carry_out, S, C, taps, pos);
     else
-        causal_conv_silu_kernel<bf16><<<grid, 128, 0, s>>>((const bf16*)in, ld_in, (bf16*)out, ld_out, w, b, carry, S, C, taps, pos);
-    if (taps > 1) {
+        causal_conv_silu_kernel<bf16><<<grid, 128, 0, s>>>((const bf16*)in, ld_in, (bf16*)out, ld_out, w, b, carry, carry_out, S, C, taps, pos);
+    if (taps > 1 && !fused) {
         count_launch();
         if (dt == DT_F32)
             conv_carry_update_kernel<float><<<(C + 127) / 128, 128, 0, s>>>((const float*)in, ld_in, carry, S, C, taps, pos);
