@@ -221,6 +221,18 @@ def test_heads_wider_than_one_tile(dim, vdim):
     assert rel(run(m, toks, [64, 129, 193] + list(range(194, 215)))[1:], want[1:]) < BF16_TOL
 
 
+def test_a_prompt_longer_than_one_pass_of_the_block_form():
+    """4300 rows in one step: the block form of the recurrence runs a second pass that starts from the state the first
+    left (a pass covers 64 blocks of 64 rows). Compared with the same prompt fed in portions of 31 rows, which all take the
+    token-by-token kernel (the one the other tests hold to the oracle)."""
+    m, d, _ = model_of("mixed")
+    toks = seq_cases.tokens(4300, d["vocab"], seed=60)
+    whole = run(m, toks, [])
+    parts = run(m, toks, range(31, 4300, 31))
+    assert rel(whole[4000:], parts[4000:].double()) < 2 * F32_TOL
+    assert rel(whole, parts.double()) < 2 * F32_TOL
+
+
 # ---- batches, pages and slots that are used again -----------------------------------------------------------------------------
 def test_a_batch_of_unequal_requests_equals_each_alone():
     m, d, _ = model_of("mixed")
