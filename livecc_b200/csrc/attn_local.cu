@@ -4,6 +4,9 @@
 //     softmax sink: p_j = exp(s_j) / (1 + sum_j exp(s_j)), and a per-head sigmoid output gate.
 // Scores, weights and the accumulation are fp32; K and V pages hold the model's storage type.
 #include <math.h>
+#include <stdlib.h>
+
+#include <algorithm>
 
 #include "common.cuh"
 #include "launch.h"
@@ -587,7 +590,14 @@ int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_p
                     int DV, int chunk, float scale, bool tensor_cores, SeqPos pos, cudaStream_t s) {
     if (!q || !k_pages || !v_pages || !page_table || !out || S < 1 || Hq < 1 || G < 1 || Hq % G || D < 1 || DV < 1)
         return -2;
-    if (S >= kAttnTiledMin) {
+    // The one-CTA-per-row kernel keeps one score per key of the longest window a row of this call can have in shared memory.
+    // Windows that do not fit (or whose length only the device knows, in a replayed step without chunks) go to the tiled
+    // kernels, which walk the keys in tiles and take any row count.
+    int max_keys = chunk > 0 ? chunk : -1;
+    if (!pos.kv_len) max_keys = chunk > 0 ? std::min(chunk, pos.past + S) : pos.past + S;
+    const size_t smem = sizeof(float) * ((size_t)D + (size_t)std::max(max_keys, 0));
+    static const bool force_tiled = [] { const char* e = getenv("LIVECC_B200_SEQ_ATTN_TILED"); return e && e[0] == '1'; }();
+    if (S >= kAttnTiledMin || max_keys < 0 || smem > 160 * 1024 || force_tiled) {
         if (dt == DT_BF16 && tensor_cores && D <= kAttnMmaMaxDim)
             return launch_attn_mma(q, k_pages, v_pages, page_table, page_size, gate, ld_gate, out, ld_out, S, Hq, G, D, DV, chunk,
                                    scale, pos, s);
@@ -597,14 +607,6 @@ int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_p
         return launch_attn_tiled<bf16>(q, k_pages, v_pages, page_table, page_size, gate, ld_gate, out, ld_out, S, Hq, G, D, DV, chunk,
                                        scale, pos, s);
     }
-    // shared memory holds one score per key of the longest window a row of this call can have
-    int max_keys = chunk;
-    if (chunk <= 0) {
-        if (pos.kv_len) return -3;  // plain causal attention needs the host-side length to size the score buffer
-        max_keys = pos.past + S;
-    }
-    const size_t smem = sizeof(float) * ((size_t)D + (size_t)max_keys);
-    if (smem > 200 * 1024) return -3;
     dim3 grid(S, Hq);
     count_launch();
     if (dt == DT_F32) {

@@ -233,6 +233,37 @@ def test_a_prompt_longer_than_one_pass_of_the_block_form():
     assert rel(whole, parts.double()) < 2 * F32_TOL
 
 
+def test_tiled_attention_kernels_take_any_row_count(monkeypatch):
+    """Windows too long for the one-CTA-per-row kernel's score buffer go to the tiled kernels whatever the row count; the
+    switch forces that route, so decode steps and portions of 2 to 15 rows run on them: fp32 tiles, and bf16 tensor-core tiles in
+    both forms (aligned head sizes, and sizes that are not multiples of 8)."""
+    from livecc_b200.seq_engine import SeqLMForCausalLM
+
+    monkeypatch.setenv("LIVECC_B200_SEQ_ATTN_TILED", "1")
+    code = ("import sys, json, torch; sys.path[:0] = [%r, %r]; import seq_cases, seq_oracle as O;"
+            "from livecc_b200.checkpoint import synthetic_seq_tensors; from livecc_b200.config import SeqModelConfig;"
+            "from livecc_b200.seq_engine import SeqLMForCausalLM\n"
+            "def rel(g, w):\n"
+            "    g, w = g.double().cpu(), w.double(); return float(((g - w).pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt().clamp_min(1e-30)).max())\n"
+            "out = {}\n"
+            "for name in ('mixed', 'odd'):\n"
+            "    d = seq_cases.CASES[name]; cfg = SeqModelConfig.from_json(d); t = synthetic_seq_tensors(cfg, seed=11)\n"
+            "    toks = seq_cases.tokens(70, d['vocab'], seed=1); want = O.forward(d, t, toks)[0]\n"
+            "    for dt in ('float32', 'bfloat16'):\n"
+            "        m = SeqLMForCausalLM.from_state_dict(cfg, t, dt); c = m.new_cache(); rows = []; lo = 0\n"
+            "        for hi in [3, 5, 20, 21, 22, 30, 45] + list(range(46, 71)):\n"
+            "            rows.append(m.forward_step([(c, toks[lo:hi])], [list(range(hi - lo))]).cpu()); lo = hi\n"
+            "        out[name + ':' + dt] = rel(torch.cat(rows), want)\n"
+            "print('RESULT ' + json.dumps(out))\n") % (os.path.dirname(os.path.abspath(__file__)), os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    # a process of its own: the library reads the switch once
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, env=dict(os.environ))
+    assert r.returncode == 0, r.stderr[-2000:]
+    res = json.loads([l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1][7:])
+    for key, err in res.items():
+        # bf16: the worst of 70 rows of the small "odd" model (no soft cap, tau = 1) sits at the edge of BF16_TOL on either route
+        assert err < (F32_TOL if key.endswith("float32") else 1.5 * BF16_TOL), (key, err)
+
+
 # ---- batches, pages and slots that are used again -----------------------------------------------------------------------------
 def test_a_batch_of_unequal_requests_equals_each_alone():
     m, d, _ = model_of("mixed")
