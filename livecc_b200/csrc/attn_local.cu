@@ -154,8 +154,9 @@ __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float*
     float* sp_ = sq_ + (size_t)dc * APQ;                                  // [AK][APQ]
     T* sk_ = reinterpret_cast<T*>(sp_ + (size_t)AK * APQ);                // [dc][APQ]
     T* sv_ = sk_ + (size_t)dc * APQ;                                      // [AK][APV]
-    // heavy (late) query tiles first: a tile's work grows with its distance from the start of its chunk
-    const int t0 = (gridDim.x - 1 - blockIdx.x) * AQ, h = blockIdx.y, c0 = blockIdx.z * AVW;
+    // heavy (late) query tiles first, for all heads, then the lighter ones: a tile's work grows with its distance from the
+    // start of its chunk, and CTAs are handed out in order of blockIdx.x, then y
+    const int t0 = (gridDim.y - 1 - blockIdx.y) * AQ, h = blockIdx.x, c0 = blockIdx.z * AVW;
     const int g = h / (Hq / G);
     const int past = seq_past(pos, S);
     const int rows = min(AQ, S - t0);
@@ -296,7 +297,7 @@ int launch_attn_tiled(const float* q, const void* k_pages, const void* v_pages, 
     static SmemAttrOnce once;
     const size_t smem = attn_tiled_smem<T>(ADC);
     if (ensure_dyn_smem(once, attn_chunk_sink_tiled_kernel<T>, (int)smem)) return -100;
-    dim3 grid((S + AQ - 1) / AQ, Hq, (DV + AVW - 1) / AVW);
+    dim3 grid(Hq, (S + AQ - 1) / AQ, (DV + AVW - 1) / AVW);
     count_launch();
     attn_chunk_sink_tiled_kernel<T><<<grid, 256, attn_tiled_smem<T>(D), s>>>(q, (const T*)k_pages, (const T*)v_pages, page_table, page_size,
                                                                             (const T*)gate, ld_gate, (T*)out, ld_out, S, Hq, G, D, DV,
@@ -336,7 +337,7 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
     constexpr int KT = KH * MK;                         // keys per step of the CTA: one 64-key tile per group of 4 warps
     bf16* sK0 = sQ + (size_t)MQ * LQ;                   // [2][KT][LQ]   (the second buffer only with VEC8)
     bf16* sV0 = sK0 + (size_t)(VEC8 ? 2 : 1) * KT * LQ; // [2][KT][MLV]
-    const int t0 = (gridDim.x - 1 - blockIdx.x) * MQ, h = blockIdx.y, c0 = blockIdx.z * MVW;
+    const int t0 = (gridDim.y - 1 - blockIdx.y) * MQ, h = blockIdx.x, c0 = blockIdx.z * MVW;
     const int g = h / (Hq / G);
     const int past = seq_past(pos, S);
     const int rows = min(MQ, S - t0);
@@ -551,7 +552,7 @@ int launch_attn_mma(const float* q, const void* k_pages, const void* v_pages, co
     const int nbuf = vec8 ? 2 : 1, kh = two ? 2 : 1;
     auto bytes = [&](int dp) { return ((size_t)MQ * (dp + 8) + (size_t)nbuf * kh * MK * (dp + 8 + MLV)) * sizeof(bf16); };
     const size_t smem = bytes(Dp), smem_max = bytes(two ? 128 : kAttnMmaMaxDim);
-    dim3 grid((S + MQ - 1) / MQ, Hq, (DV + MVW - 1) / MVW);
+    dim3 grid(Hq, (S + MQ - 1) / MQ, (DV + MVW - 1) / MVW);
     count_launch();
 #define LCC_ATTN_MMA(ONCE, VEC, KHN)                                                                                         \
     do {                                                                                                                     \
