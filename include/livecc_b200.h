@@ -301,6 +301,13 @@ int lcc_resize_bicubic_aa_u8(lcc_ctx* ctx, const lcc_resize_plan* plan, const ui
 #define LCC_DT_F32 1
 #define LCC_MIX_SSD 1      /* scalar-decay state-space layer: in-proj -> causal conv + silu -> recurrence -> gated grouped norm -> out-proj */
 #define LCC_MIX_PARALLEL 2 /* chunk-local sink attention (left) beside gated linear attention (right), averaged after a norm each */
+#define LCC_MIX_RETENTION 3 /* rotary q/k -> linear attention with a fixed decay per head, no normaliser -> unit-rms heads x silu gate -> out-proj */
+#define LCC_MIX_LATENT 4    /* causal softmax attention over a cached low-rank latent + one shared rotary key part, per-head sink and sigmoid gate */
+#define LCC_FF_GLU 0        /* dense gated feed-forward: gelu_tanh(gate) * up */
+#define LCC_FF_MOE 1        /* routed experts (sigmoid router, top-k of score + correction, relu^2 experts) + gated shared expert */
+#define LCC_BLOCK_POSTNORM 0 /* x <- norm(alpha * x + sublayer(x)) */
+#define LCC_BLOCK_PRENORM_HC 1 /* `streams` residual streams x_s; per sublayer: u = sum_s in[s] x_s; y = sublayer(norm(u));
+                                  x_t <- sum_s mix[s][t] x_s + out[t] y. The model's output is the sum of the streams. */
 
 typedef struct {
     int32_t type; /* LCC_MIX_* */
@@ -313,6 +320,18 @@ typedef struct {
     /* LCC_MIX_PARALLEL, right: heads x dim key channels, heads x vdim value channels, decay bottleneck rank, temperature tau */
     int32_t r_heads, r_dim, r_vdim, r_rank;
     float r_tau;
+    /* LCC_MIX_RETENTION: heads x dim key channels (the first t_rot_dims of each head rotated), heads x vdim value channels */
+    int32_t t_heads, t_dim, t_vdim, t_rot_dims;
+    /* LCC_MIX_LATENT: per head a_dim unrotated + a_rot_dim rotated query channels, value size a_vdim; the cache holds
+     * a_rank latent channels + a_rot_dim rotated key channels per token; a_kv_from >= 0: this layer has no cache of its own
+     * and reads that layer's */
+    int32_t a_heads, a_dim, a_rot_dim, a_vdim, a_rank, a_kv_from;
+    float a_scale;
+    float rot_mag;  /* factor on cos and sin of the rotation (1 without long-context scaling) */
+    /* feed-forward: ff_kind LCC_FF_*; MoE: e_experts experts of width e_ff, e_top per token, weights = score * e_scale,
+     * shared expert of width e_shared_ff (0 = none) */
+    int32_t ff_kind, e_experts, e_top, e_ff, e_shared_ff;
+    float e_scale;
     /* weights: matrices [out, in] in the model's storage type; everything named *_f32 is fp32 */
     const float *norm1_f32, *norm2_f32;
     const void* s_in;          /* [2*inner + 2*groups*state + heads, width], rows [z | x | B | C | dt] */
@@ -333,6 +352,25 @@ typedef struct {
     const float* r_branch_norm_f32; /* [width] */
     const void* ff_in;         /* [2*ff, width], rows [gate | up]; act = gelu_tanh(gate) * up */
     const void* ff_out;        /* [width, ff] */
+    const float* rot_inv_freq_f32; /* [rot dims / 2]: rotation frequencies of this layer's mixer, computed by the host */
+    const void* t_in;          /* [2*heads*dim + 2*heads*vdim, width], rows [q | k | v | gate] */
+    const float* t_log_decay_f32; /* [heads]: log of the per-head decay */
+    const float* t_norm_f32;   /* [vdim]: weight of the per-head unit norm (ones when the design has none) */
+    const void* t_out;         /* [width, heads*vdim] */
+    const void* a_in;          /* [heads*(dim+rot_dim) (+ rank + rot_dim) + heads, width], rows [q | latent, key part | gate];
+                                  a layer that reads another layer's cache has no middle block */
+    const float* a_latent_norm_f32; /* [rank] */
+    const void* a_uk_t;        /* [heads][rank][dim]: each head's key up-projection, transposed (query absorption) */
+    const void* a_uv;          /* [heads*vdim, rank] */
+    const float* a_sink_f32;   /* [heads] sink logits */
+    const void* a_out;         /* [width, heads*vdim] */
+    const void* e_router;      /* [experts (+1), width]: router rows, then the shared expert's gate row */
+    const float* e_correction_f32; /* [experts]: added to the scores for the choice only */
+    const void* e_up;          /* [experts][e_ff, width] */
+    const void* e_down;        /* [experts][width, e_ff] */
+    const void* e_shared_up;   /* [e_shared_ff, width] */
+    const void* e_shared_down; /* [width, e_shared_ff] */
+    const float *hc1_f32, *hc2_f32; /* LCC_BLOCK_PRENORM_HC: [in: s | out: s | mix: s*s, indexed from*s + to] per sublayer */
 } lcc_seq_layer;
 
 typedef struct {
@@ -340,8 +378,10 @@ typedef struct {
     int32_t rows_padded8; /* non-zero: every matrix is allocated with its row count rounded up to 8 (zero rows), so that a
                              ragged projection can run as an 8-aligned tensor-core GEMM into its padded output buffer */
     float eps, alpha, embed_scale, logit_softcap; /* logit_softcap <= 0: none */
+    int32_t block;   /* LCC_BLOCK_* */
+    int32_t streams; /* residual streams of LCC_BLOCK_PRENORM_HC (>= 1) */
     const void* embed;          /* [vocab, width] */
-    const float* inv_freq_f32;  /* [width/2]: sinusoidal position frequencies, computed by the host */
+    const float* inv_freq_f32;  /* [width/2]: sinusoidal position frequencies, computed by the host; NULL: the embedding has no position term */
     const float* final_norm_f32;
     const void* head;           /* [vocab, width] */
     const lcc_seq_layer* layers;
@@ -349,8 +389,10 @@ typedef struct {
 
 /* One sequence's part of a step: n_new tokens that follow `past` cached ones. layer_state[i]: this sequence's fp32 state
  * slot of layer i (SSD: [conv carry: channels x (conv-1)] then [heads x vdim x state]; PARALLEL: [heads x vdim x dim] of
- * the right mixer), zero at the start of a sequence. k_pages[i] / v_pages[i]: the layer's page pools
- * [page][kv_heads][page_size][dim|vdim] (NULL for layers without attention); page_table: logical -> physical page.
+ * the right mixer; RETENTION: [heads x vdim x dim]), zero at the start of a sequence. k_pages[i] / v_pages[i]: the layer's page pools
+ * [page][kv_heads][page_size][dim|vdim] (NULL for layers without attention); a LATENT layer has K pages only,
+ * [page][1][page_size][rank + rot_dim], and a layer that reads another layer's cache is given that layer's pool.
+ * page_table: logical -> physical page.
  * scalars (optional, device int32[LCC_SC_COUNT]): when given, kernels read the number of cached tokens from scalars[LCC_SC_KV_LEN]
  * and the ids from ids[scalars[LCC_SC_SEQ_LEN] - n_new ...], and do nothing once scalars[LCC_SC_FINISHED] is set, so that a
  * decode step can be replayed from a CUDA graph; otherwise `past` and ids[0..n_new) are used. */

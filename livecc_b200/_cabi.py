@@ -70,16 +70,24 @@ class SeqLayer(C.Structure):
                                          "l_heads", "l_kv_heads", "l_dim", "l_vdim", "l_chunk")] + \
                [("l_scale", C.c_float)] + [(n, C.c_int32) for n in ("r_heads", "r_dim", "r_vdim", "r_rank")] + \
                [("r_tau", C.c_float)] + \
+               [(n, C.c_int32) for n in ("t_heads", "t_dim", "t_vdim", "t_rot_dims", "a_heads", "a_dim", "a_rot_dim", "a_vdim",
+                                         "a_rank", "a_kv_from")] + [("a_scale", C.c_float), ("rot_mag", C.c_float)] + \
+               [(n, C.c_int32) for n in ("ff_kind", "e_experts", "e_top", "e_ff", "e_shared_ff")] + [("e_scale", C.c_float)] + \
                [(n, C.c_void_p) for n in ("norm1_f32", "norm2_f32", "s_in", "s_conv_w_f32", "s_conv_b_f32", "s_dt_bias_f32",
                                           "s_a_log_f32", "s_skip_f32", "s_norm_f32", "s_out", "l_in", "l_in_bias_f32", "l_in_bias",
                                           "l_qnorm_f32", "l_knorm_f32", "l_out", "l_branch_norm_f32", "r_in", "r_decay_up",
-                                          "r_decay_bias_f32", "r_norm_f32", "r_out", "r_branch_norm_f32", "ff_in", "ff_out")]
+                                          "r_decay_bias_f32", "r_norm_f32", "r_out", "r_branch_norm_f32", "ff_in", "ff_out",
+                                          "rot_inv_freq_f32", "t_in", "t_log_decay_f32", "t_norm_f32", "t_out", "a_in",
+                                          "a_latent_norm_f32", "a_uk_t", "a_uv", "a_sink_f32", "a_out", "e_router",
+                                          "e_correction_f32", "e_up", "e_down", "e_shared_up", "e_shared_down", "hc1_f32",
+                                          "hc2_f32")]
 
 
 class SeqModelDesc(C.Structure):
     """lcc_seq_model_desc"""
     _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("dtype", C.c_int32),
                 ("rows_padded8", C.c_int32), ("eps", C.c_float), ("alpha", C.c_float), ("embed_scale", C.c_float), ("logit_softcap", C.c_float),
+                ("block", C.c_int32), ("streams", C.c_int32),
                 ("embed", C.c_void_p), ("inv_freq_f32", C.c_void_p), ("final_norm_f32", C.c_void_p), ("head", C.c_void_p),
                 ("layers", C.POINTER(SeqLayer))]
 
@@ -92,7 +100,9 @@ class SeqEntry(C.Structure):
 
 
 DT_BF16, DT_F32 = 0, 1
-MIX_SSD, MIX_PARALLEL = 1, 2
+MIX_SSD, MIX_PARALLEL, MIX_RETENTION, MIX_LATENT = 1, 2, 3, 4
+FF_GLU, FF_MOE = 0, 1
+BLOCK_POSTNORM, BLOCK_PRENORM_HC = 0, 1
 
 _libs = {}   # profile (None = the full library) -> CDLL
 

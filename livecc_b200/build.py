@@ -21,7 +21,8 @@ OBJ_DIR = PKG_DIR / "build"
 # A profile is the subset of csrc/*.cu one model family needs; it links into a library of its own, so that serving that
 # family alone compiles nothing else. The full library (profile None) holds every source and exports a superset.
 PROFILES = {
-    "seq": ["cabi_core", "gemm_tcgen05", "sampling", "linear_any", "recurrent", "recurrent_chunked", "attn_local", "rowops", "seq_model"],
+    "seq": ["cabi_core", "gemm_tcgen05", "sampling", "linear_any", "recurrent", "recurrent_chunked", "attn_local", "rowops", "rotary", "attn_latent",
+            "hyper", "moe", "seq_model"],
 }
 
 

@@ -313,15 +313,33 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor]) -> None:
 
 def seq_param_specs(cfg) -> List[Tuple[str, Tuple[int, ...], str]]:
     """(name, shape, kind) of every tensor of a hybrid sequence model (config.SeqModelConfig); kind picks the synthetic
-    fill: 'w' matrix, 'b' bias, 'norm' norm weight, 'conv' taps, 'dt' step bias, 'alog' log decay rate, 'skip'."""
+    fill: 'w' matrix, 'b' bias, 'norm' norm weight, 'conv' taps, 'dt' step bias, 'alog' log decay rate, 'skip',
+    'hc_in' / 'hc_out' / 'hc_mix' stream weights (spread around 1/streams, 1 and a perturbed identity)."""
     W = cfg.width
     specs = [("embed", (cfg.vocab, W), "embed")]
+    hc = getattr(cfg, "block", "postnorm") == "prenorm_hc"
+    norm = "norm0" if getattr(cfg, "norm_offset", 0.0) else "norm"   # weights stored around zero
     for i, L in enumerate(cfg.layers):
         p = f"l{i}."
-        specs.append((p + "norm1", (W,), "norm"))
-        if L.ff:
-            specs.append((p + "norm2", (W,), "norm"))
-        if L.type == "mamba2":
+        specs.append((p + "norm1", (W,), norm))
+        if L.ff or L.moe:
+            specs.append((p + "norm2", (W,), norm))
+        if hc:
+            n = cfg.streams
+            for q in ("hc1.", "hc2.") if (L.ff or L.moe) else ("hc1.",):
+                specs += [(p + q + "in", (n,), "hc_in"), (p + q + "out", (n,), "hc_out"), (p + q + "mix", (n, n), "hc_mix")]
+        if L.type == "retention":
+            t, m = L.retention, p + "mix."
+            specs += [(m + "q", (t.heads * t.dim, W), "w"), (m + "k", (t.heads * t.dim, W), "w"), (m + "v", (t.heads * t.vdim, W), "w"),
+                      (m + "g", (t.heads * t.vdim, W), "w"), (m + "o", (W, t.heads * t.vdim), "w")]
+        elif L.type == "latent_attention":
+            a, m = L.latent, p + "mix."
+            specs.append((m + "q", (a.heads * (a.dim + a.rot_dim), W), "w"))
+            if a.kv_from < 0:
+                specs += [(m + "dkv", (a.kv_rank + a.rot_dim, W), "w"), (m + "dkv.norm", (a.kv_rank,), "norm")]
+            specs += [(m + "uk", (a.heads * a.dim, a.kv_rank), "w"), (m + "uv", (a.heads * a.vdim, a.kv_rank), "w"),
+                      (m + "sink", (a.heads,), "skip"), (m + "g", (a.heads, W), "w"), (m + "o", (W, a.heads * a.vdim), "w")]
+        elif L.type == "mamba2":
             s, m = L.ssd, p + "mix."
             specs += [(m + "in", (s.proj_rows, W), "w"), (m + "conv", (s.conv_channels, s.conv), "conv"),
                       (m + "conv.b", (s.conv_channels,), "b"), (m + "dt_bias", (s.heads,), "dt"), (m + "A_log", (s.heads,), "alog"),
@@ -340,9 +358,17 @@ def seq_param_specs(cfg) -> List[Tuple[str, Tuple[int, ...], str]]:
                       (b + "o", (W, r.heads * r.vdim), "w"), (b + "norm", (r.vdim,), "norm"), (b + "a1", (rank, W), "w"),
                       (b + "a2", (r.heads * r.dim, rank), "w"), (b + "a2.b", (r.heads * r.dim,), "decay_b"),
                       (a + "out", (W,), "norm"), (b + "out", (W,), "norm")]
-        if L.ff:
+        if L.moe:
+            e, m = L.moe, p + "mlp."
+            for j in range(e.experts):
+                specs += [(f"{m}e{j}.up", (e.ff, W), "w"), (f"{m}e{j}.down", (W, e.ff), "w")]
+            specs += [(m + "router", (e.experts, W), "w"), (m + "correction", (e.experts,), "b")]
+            if e.shared_ff:
+                specs += [(m + "shared.up", (e.shared_ff, W), "w"), (m + "shared.down", (W, e.shared_ff), "w"),
+                          (m + "shared.sg", (1, W), "w")]
+        elif L.ff:
             specs += [(p + "mlp.gate", (L.ff, W), "w"), (p + "mlp.up", (L.ff, W), "w"), (p + "mlp.down", (W, L.ff), "w")]
-    specs += [("final.norm", (W,), "norm"), ("head", (cfg.vocab, W), "w")]
+    specs += [("final.norm", (W,), norm), ("head", (cfg.vocab, W), "w")]
     return specs
 
 
@@ -362,6 +388,14 @@ def synthetic_seq_tensors(cfg, seed: int = 1234, device="cpu") -> Dict[str, torc
             t = u * 3.4641
         elif kind == "norm":
             t = 1.0 + 0.5 * u
+        elif kind == "norm0":
+            t = 0.5 * u
+        elif kind == "hc_in":
+            t = (1.0 + u) / shape[0]
+        elif kind == "hc_out":
+            t = 1.0 + 0.6 * u
+        elif kind == "hc_mix":
+            t = torch.eye(shape[0], device=u.device) + 0.4 * u
         elif kind == "conv":
             t = u * 1.5
         elif kind == "dt":

@@ -171,12 +171,105 @@ class GlaConfig:
 
 
 @dataclass
+class RotaryConfig:
+    """Rotate-half rotary positions on the first `dims` channels of a head: pair i turns by p * base^(-2i/dims). `scaling`
+    (factor, original, fast, slow) interpolates the slow pairs for contexts beyond `original` positions (YaRN: pairs that
+    turn fewer than `slow` times over the original context are divided by `factor`, pairs that turn more than `fast` times
+    are kept, a linear ramp in between) and multiplies cos and sin by 0.1 ln(factor) + 1."""
+    dims: int
+    base: float
+    scaling: dict = None
+
+    @staticmethod
+    def from_json(d: dict) -> "RotaryConfig":
+        sc = d.get("scaling")
+        return RotaryConfig(dims=int(d["dims"]), base=float(d["base"]),
+                            scaling={k: float(sc[k]) for k in ("factor", "original", "fast", "slow")} if sc else None)
+
+    def to_json(self) -> dict:
+        out = dict(dims=self.dims, base=self.base)
+        if self.scaling:
+            out["scaling"] = dict(self.scaling)
+        return out
+
+    def frequencies(self):
+        """([dims/2] frequencies in float64, factor on cos and sin)."""
+        import math
+
+        half = self.dims // 2
+        f = [self.base ** (-2.0 * i / self.dims) for i in range(half)]
+        if not self.scaling:
+            return f, 1.0
+        sc = self.scaling
+        log_base = math.log(self.base)
+
+        def pair_index(turns):   # the (fractional) pair that makes `turns` full turns over the original context
+            return self.dims * math.log(sc["original"] / (2.0 * math.pi * turns)) / (2.0 * log_base)
+
+        lo = max(math.floor(pair_index(sc["fast"])), 0)
+        hi = min(math.ceil(pair_index(sc["slow"])), self.dims - 1)
+        out = []
+        for i in range(half):
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f[i] / sc["factor"] * ramp + f[i] * (1.0 - ramp))
+        return out, 0.1 * math.log(sc["factor"]) + 1.0
+
+
+@dataclass
+class RetentionConfig:
+    """Linear attention with one fixed decay per head and no normaliser: S <- decay_h S + k v^T, o = S^T q; rotary q and k,
+    k scaled by dim^-1/2; each head's output brought to unit rms, times silu(gate)."""
+    heads: int
+    dim: int
+    vdim: int
+    decay: list
+    rot: RotaryConfig
+
+
+@dataclass
+class LatentAttnConfig:
+    """Causal softmax attention whose keys and values are per-head up-projections of a cached latent of `kv_rank` channels,
+    plus `rot_dim` rotary channels shared by all heads; a per-head sink logit in the denominator and a per-head sigmoid
+    gate. `kv_from` >= 0: the layer has no latent projection and reads that layer's cache."""
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    scale: float
+    rot: RotaryConfig
+    kv_from: int = -1
+
+
+@dataclass
+class MoeConfig:
+    """Routed feed-forward: `experts` relu^2 experts of width `ff`, `top` per token chosen by sigmoid score + correction,
+    weighted by score * scale; a shared expert of width `shared_ff` (0: none) behind a scalar sigmoid gate."""
+    experts: int
+    top: int
+    ff: int
+    scale: float = 1.0
+    shared_ff: int = 0
+
+
+@dataclass
 class SeqLayerConfig:
-    type: str                      # "mamba2" | "parallel"
+    type: str                      # "mamba2" | "parallel" | "retention" | "latent_attention"
     ssd: SsdMixerConfig = None
     left: ChunkAttnConfig = None
     right: GlaConfig = None
-    ff: int = 0                    # 0 = the layer has no feed-forward
+    ff: int = 0                    # 0 = the layer has no dense feed-forward
+    retention: RetentionConfig = None
+    latent: LatentAttnConfig = None
+    moe: MoeConfig = None          # routed feed-forward instead of the dense one
+
+
+# What an architecture name fixes (everything else comes from config.json): the residual block form, whether the stored
+# norm weights are centred on zero (the applied weight is 1 + w), and the position term of the embedding.
+SEQ_FAMILIES = {
+    "Bimopel": dict(block="postnorm", norm_offset=0.0, positions="sinusoid"),
+    "Kedelorn": dict(block="prenorm_hc", norm_offset=1.0, positions=None),
+}
 
 
 @dataclass
@@ -190,22 +283,47 @@ class SeqModelConfig:
     embed_scale: float = 1.0
     logit_softcap: float = 0.0
     eos_token_id: int = -1         # none unless config.json names one
+    block: str = "postnorm"        # "postnorm" | "prenorm_hc" (pre-norm sublayers on `streams` residual streams)
+    streams: int = 1
+    norm_offset: float = 0.0       # added to every stored layer-norm weight (1.0: weights stored around zero)
+    positions: str = "sinusoid"    # position term of the embedding, or None
 
     @staticmethod
     def from_json(d: dict) -> "SeqModelConfig":
         """config.json of a hybrid sequence model: `layers` lists each layer's `type`, its mixer's sizes and its `mlp`."""
+        arch = d.get("architecture", "Bimopel")
+        if arch not in SEQ_FAMILIES:
+            raise NotImplementedError(f"architecture {arch!r} is not a hybrid sequence model (known: {sorted(SEQ_FAMILIES)})")
+        fam = SEQ_FAMILIES[arch]
         layers = []
         for i, L in enumerate(d["layers"]):
             mx, mlp = L["mixer"], L.get("mlp")
-            ff = 0
+            ff, moe = 0, None
             if mlp is not None:
-                if mlp.get("kind", "dense") != "dense":
-                    raise NotImplementedError(f"layer {i}: feed-forward kind {mlp.get('kind')!r} is not supported")
-                ff = int(mlp["ff"])
-            if L["type"] == "mamba2":
+                kind = mlp.get("kind", "dense")
+                if kind == "dense":
+                    ff = int(mlp["ff"])
+                elif kind == "moe":
+                    r, sh = mlp["router"], mlp.get("shared")
+                    moe = MoeConfig(experts=int(r["experts"]), top=int(r["top"]), ff=int(mlp["expert"]["ff"]),
+                                    scale=float(r.get("scale", 1.0)), shared_ff=int(sh["ff"]) if sh else 0)
+                else:
+                    raise NotImplementedError(f"layer {i}: feed-forward kind {kind!r} is not supported")
+            if L["type"] == "retention":
+                rot = RotaryConfig.from_json(mx["rot"]) if mx.get("rot") else RotaryConfig(0, 10000.0)
+                layers.append(SeqLayerConfig("retention", ff=ff, moe=moe, retention=RetentionConfig(
+                    heads=int(mx["heads"]), dim=int(mx["dim"]), vdim=int(mx.get("vdim", mx["dim"])),
+                    decay=[float(x) for x in mx["decay"]], rot=rot)))
+            elif L["type"] == "latent_attention":
+                src = mx.get("kv_from")
+                layers.append(SeqLayerConfig("latent_attention", ff=ff, moe=moe, latent=LatentAttnConfig(
+                    heads=int(mx["heads"]), dim=int(mx["dim"]), rot_dim=int(mx["rot_dim"]), vdim=int(mx.get("vdim", mx["dim"])),
+                    kv_rank=int(mx["kv_rank"]), scale=float(mx["scale"]), rot=RotaryConfig.from_json(mx["rot"]),
+                    kv_from=-1 if src is None else int(src))))
+            elif L["type"] == "mamba2":
                 layers.append(SeqLayerConfig("mamba2", ssd=SsdMixerConfig(
                     heads=int(mx["heads"]), vdim=int(mx["vdim"]), state=int(mx["state"]), groups=int(mx.get("groups", 1)),
-                    conv=int(mx.get("conv", 4)), norm_groups=int(mx.get("norm_groups", 1))), ff=ff))
+                    conv=int(mx.get("conv", 4)), norm_groups=int(mx.get("norm_groups", 1))), ff=ff, moe=moe))
             elif L["type"] == "parallel":
                 l, r = mx["left"], mx["right"]
                 left = ChunkAttnConfig(heads=int(l["heads"]), kv_heads=int(l.get("kv_heads", l["heads"])), dim=int(l["dim"]),
@@ -213,14 +331,15 @@ class SeqModelConfig:
                                        scale=float(l.get("scale", float(l["dim"]) ** -0.5)))
                 right = GlaConfig(heads=int(r["heads"]), dim=int(r["dim"]), vdim=int(r.get("vdim", r["dim"])),
                                   tau=float(r.get("tau", 1.0)))
-                layers.append(SeqLayerConfig("parallel", left=left, right=right, ff=ff))
+                layers.append(SeqLayerConfig("parallel", left=left, right=right, ff=ff, moe=moe))
             else:
                 raise NotImplementedError(f"layer {i}: mixer type {L['type']!r} is not supported")
         return SeqModelConfig(
-            architecture=d.get("architecture", "Bimopel"), vocab=int(d["vocab"]), width=int(d["width"]), layers=layers,
+            architecture=arch, vocab=int(d["vocab"]), width=int(d["width"]), layers=layers,
             eps=float((d.get("norm") or {}).get("eps", 1e-5)), alpha=float(d.get("postln_alpha", 1.0)),
             embed_scale=float((d.get("embedding") or {}).get("scale", 1.0)), logit_softcap=float(d.get("logit_softcap") or 0.0),
-            eos_token_id=int(d.get("eos_token_id", -1)))
+            eos_token_id=int(d.get("eos_token_id", -1)), block=fam["block"], streams=int(d.get("streams", 1)),
+            norm_offset=fam["norm_offset"], positions=fam["positions"])
 
     def to_json(self) -> dict:
         """The inverse of from_json (used to write synthetic checkpoints)."""
@@ -229,22 +348,57 @@ class SeqModelConfig:
             if L.type == "mamba2":
                 s = L.ssd
                 mx = dict(heads=s.heads, vdim=s.vdim, state=s.state, groups=s.groups, conv=s.conv, norm_groups=s.norm_groups)
+            elif L.type == "retention":
+                t = L.retention
+                mx = dict(heads=t.heads, dim=t.dim, vdim=t.vdim, decay=list(t.decay), rot=t.rot.to_json())
+            elif L.type == "latent_attention":
+                a = L.latent
+                mx = dict(heads=a.heads, dim=a.dim, rot_dim=a.rot_dim, vdim=a.vdim, kv_rank=a.kv_rank, scale=a.scale, rot=a.rot.to_json())
+                if a.kv_from >= 0:
+                    mx["kv_from"] = a.kv_from
             else:
                 l, r = L.left, L.right
                 mx = dict(left=dict(heads=l.heads, kv_heads=l.kv_heads, dim=l.dim, vdim=l.vdim, mask=dict(size=l.chunk), scale=l.scale),
                           right=dict(heads=r.heads, dim=r.dim, vdim=r.vdim, tau=r.tau))
-            out.append(dict(type=L.type, mixer=mx, mlp=dict(ff=L.ff, kind="dense") if L.ff else None))
+            mlp = dict(ff=L.ff, kind="dense") if L.ff else None
+            if L.moe:
+                e = L.moe
+                mlp = dict(kind="moe", expert=dict(ff=e.ff), router=dict(experts=e.experts, top=e.top, scale=e.scale))
+                if e.shared_ff:
+                    mlp["shared"] = dict(ff=e.shared_ff)
+            out.append(dict(type=L.type, mixer=mx, mlp=mlp))
+        if self.block == "prenorm_hc":
+            return dict(architecture=self.architecture, vocab=self.vocab, width=self.width, streams=self.streams, layers=out,
+                        norm=dict(eps=self.eps))
         return dict(architecture=self.architecture, vocab=self.vocab, width=self.width, layers=out, norm=dict(eps=self.eps),
                     postln_alpha=self.alpha, embedding=dict(scale=self.embed_scale), logit_softcap=self.logit_softcap)
 
     def validate(self) -> None:
         if self.width < 1 or self.vocab < 1:
             raise ValueError("width and vocab must be positive")
+        if self.block == "prenorm_hc" and not 1 <= self.streams <= 8:
+            raise ValueError("1 to 8 residual streams")
         for i, L in enumerate(self.layers):
+            if L.moe and not (1 <= L.moe.top <= L.moe.experts <= 512):
+                raise ValueError(f"layer {i}: unsupported router sizes {L.moe}")
             if L.type == "mamba2":
                 s = L.ssd
                 if s.heads % s.groups or s.inner % s.norm_groups or not 1 <= s.conv <= 8 or s.state > 512:
                     raise ValueError(f"layer {i}: unsupported state-space sizes {s}")
+            elif L.type == "retention":
+                t = L.retention
+                if len(t.decay) != t.heads or t.dim > 512 or t.rot.dims % 2 or t.rot.dims > t.dim or \
+                        any(not 0.0 < x <= 1.0 for x in t.decay):
+                    raise ValueError(f"layer {i}: unsupported retention sizes {t}")
+            elif L.type == "latent_attention":
+                a = L.latent
+                if a.rot.dims != a.rot_dim or a.rot_dim % 2 or a.rot_dim < 2:
+                    raise ValueError(f"layer {i}: the rotated part of a latent-attention head is rot_dim = rot.dims (even) channels")
+                if a.kv_from >= 0:
+                    o = self.layers[a.kv_from] if a.kv_from < i else None
+                    if o is None or o.type != "latent_attention" or o.latent.kv_from >= 0 or \
+                            (o.latent.kv_rank, o.latent.rot_dim, o.latent.rot) != (a.kv_rank, a.rot_dim, a.rot):
+                        raise ValueError(f"layer {i}: kv_from must name an earlier latent-attention layer with its own cache and the same geometry")
             else:
                 if L.left.heads % L.left.kv_heads or L.right.dim > 512:
                     raise ValueError(f"layer {i}: unsupported attention sizes")

@@ -1,7 +1,7 @@
 // Chunk-local attention over a paged K/V cache with arbitrary head sizes:
 //   * q/k RMS norm over the whole projection (all heads at once) and the append of k, v to the pages,
 //   * attention of new rows over the keys of their own chunk (chunks counted from position 0 of the sequence) with a
-//     softmax sink: p_j = exp(s_j) / (1 + sum_j exp(s_j)), and a per-head sigmoid output gate.
+//     softmax sink: p_j = exp(s_j) / (exp(sink_h) + sum_j exp(s_j)) (sink_h = 0 unless given), and a per-head sigmoid output gate.
 // Scores, weights and the accumulation are fp32; K and V pages hold the model's storage type.
 #include <math.h>
 #include <stdlib.h>
@@ -64,11 +64,13 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_kernel(const float* __res
                                                               const T* __restrict__ v_pages, const int* __restrict__ page_table,
                                                               int page_size, const T* __restrict__ gate, int ld_gate,
                                                               T* __restrict__ out, int ld_out, int S, int Hq, int G, int D, int DV,
-                                                              int chunk, float scale, SeqPos pos) {
+                                                              int chunk, float scale, SeqPos pos,
+                                                              const float* __restrict__ sink, int ld_v) {
     if (seq_done(pos)) return;
     extern __shared__ float sm[];
     __shared__ float red[32];
     const int t = blockIdx.x, h = blockIdx.y;
+    const float sk = sink ? sink[h] : 0.f;
     const int g = h / (Hq / G);
     const int p = seq_past(pos, S) + t;
     const int start = chunk > 0 ? (p / chunk) * chunk : 0;
@@ -79,7 +81,7 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_kernel(const float* __res
     for (int i = threadIdx.x; i < D; i += blockDim.x) sq[i] = q[((size_t)t * Hq + h) * D + i];
     __syncthreads();
     // scores: one warp per key, lanes over the head dimension
-    float mx = 0.f;  // the sink's score
+    float mx = sk;  // the sink's score
     for (int jk = warp; jk < nkeys; jk += nwarps) {
         const int pj = start + jk;
         const T* kr = k_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * D;
@@ -102,14 +104,14 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_kernel(const float* __res
         sum += e;
     }
     sum = block_sum(sum, red);   // contains the barrier that publishes sc[]
-    const float inv = 1.f / (expf(-mx) + sum);
+    const float inv = 1.f / (expf(sk - mx) + sum);
     float gv = 1.f;
     if (gate) gv = 1.f / (1.f + expf(-ldf(gate + (size_t)t * ld_gate + h)));
     for (int c = threadIdx.x; c < DV; c += blockDim.x) {
         float acc = 0.f;
         for (int jk = 0; jk < nkeys; ++jk) {
             const int pj = start + jk;
-            const T* vr = v_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * DV;
+            const T* vr = v_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * ld_v;
             acc = fmaf(sc[jk], ldf(vr + c), acc);
         }
         stf(out + (size_t)t * ld_out + (size_t)h * DV + c, acc * inv * gv);
@@ -146,7 +148,8 @@ __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float*
                                                                     const T* __restrict__ v_pages, const int* __restrict__ page_table,
                                                                     int page_size, const T* __restrict__ gate, int ld_gate,
                                                                     T* __restrict__ out, int ld_out, int S, int Hq, int G, int D, int DV,
-                                                                    int chunk, float scale, SeqPos pos) {
+                                                                    int chunk, float scale, SeqPos pos,
+                                                                    const float* __restrict__ sink, int ld_v) {
     if (seq_done(pos)) return;
     extern __shared__ __align__(16) uint8_t smem_attn[];
     const int dc = min(D, ADC);
@@ -170,7 +173,8 @@ __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float*
         p_row[i] = pf + tm + i;
         lo_row[i] = chunk > 0 ? (p_row[i] / chunk) * chunk : 0;
     }
-    float m[4] = {0.f, 0.f, 0.f, 0.f}, l[4] = {1.f, 1.f, 1.f, 1.f};
+    const float sk = sink ? sink[blockIdx.x] : 0.f;
+    float m[4] = {sk, sk, sk, sk}, l[4] = {1.f, 1.f, 1.f, 1.f};
     float o[4][8] = {};
     const float* qh = q + ((size_t)t0 * Hq + h) * D;
     const bool q_once = D <= ADC;
@@ -209,7 +213,7 @@ __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float*
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int r = lr + 16 * j;
-                    const T* vr = v_pages + row_off[j] * DV + c0;
+                    const T* vr = v_pages + row_off[j] * ld_v + c0;
                     if (r < nk) {
 #pragma unroll 8
                         for (int c = lc; c < AVW; c += 16) sv_[r * APV + c] = c0 + c < DV ? vr[c] : T(0.f);
@@ -293,7 +297,7 @@ __global__ void __launch_bounds__(256) attn_chunk_sink_tiled_kernel(const float*
 template <typename T>
 int launch_attn_tiled(const float* q, const void* k_pages, const void* v_pages, const int* page_table, int page_size,
                       const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D, int DV, int chunk,
-                      float scale, SeqPos pos, cudaStream_t s) {
+                      float scale, SeqPos pos, cudaStream_t s, const float* sink, int ld_v) {
     static SmemAttrOnce once;
     const size_t smem = attn_tiled_smem<T>(ADC);
     if (ensure_dyn_smem(once, attn_chunk_sink_tiled_kernel<T>, (int)smem)) return -100;
@@ -301,7 +305,7 @@ int launch_attn_tiled(const float* q, const void* k_pages, const void* v_pages, 
     count_launch();
     attn_chunk_sink_tiled_kernel<T><<<grid, 256, attn_tiled_smem<T>(D), s>>>(q, (const T*)k_pages, (const T*)v_pages, page_table, page_size,
                                                                             (const T*)gate, ld_gate, (T*)out, ld_out, S, Hq, G, D, DV,
-                                                                            chunk, scale, pos);
+                                                                            chunk, scale, pos, sink, ld_v);
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 
@@ -329,7 +333,8 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
                                                                   const bf16* __restrict__ v_pages, const int* __restrict__ page_table,
                                                                   int page_size, const bf16* __restrict__ gate, int ld_gate,
                                                                   bf16* __restrict__ out, int ld_out, int S, int Hq, int G, int D, int DV,
-                                                                  int chunk, float scale, SeqPos pos) {
+                                                                  int chunk, float scale, SeqPos pos,
+                                                                  const float* __restrict__ sink, int ld_v) {
     if (seq_done(pos)) return;
     extern __shared__ __align__(16) uint8_t smem_attn[];
     const int Dp = (D + 15) / 16 * 16, LQ = Dp + 8;
@@ -359,7 +364,8 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
         p_row[i] = pf + r_lo + 8 * i;
         lo_row[i] = chunk > 0 ? (p_row[i] / chunk) * chunk : 0;
     }
-    float m[2] = {0.f, 0.f};
+    const float sk = sink ? sink[blockIdx.x] : 0.f;
+    float m[2] = {sk, sk};
     // per-thread partial sums; the sink's 1 is counted once per row (by one thread of the first group of warps)
     float l[2] = {(tq == 0 && kh == 0) ? 1.f : 0.f, (tq == 0 && kh == 0) ? 1.f : 0.f};
     float o[16][4] = {};
@@ -382,7 +388,7 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
                 } else {
                     const int c = (cu - kpr) * 8;
                     const bool ok = row_ok && c < dvv;
-                    cp_async16(dV + (size_t)r * MLV + c, ok ? v_pages + ro * DV + c0 + c : v_pages, ok);
+                    cp_async16(dV + (size_t)r * MLV + c, ok ? v_pages + ro * ld_v + c0 + c : v_pages, ok);
                 }
             }
             pj += nw; slot += nw;
@@ -408,7 +414,7 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
             };
             auto vrow = [&](int r) -> const bf16* {
                 const int pj = kc + r;
-                return pj <= pl ? v_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * DV + c0 : nullptr;
+                return pj <= pl ? v_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * ld_v + c0 : nullptr;
             };
             __syncthreads();
             stage_bf16_rows(sK0, LQ, Dp, D, krow);
@@ -541,11 +547,11 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
 
 int launch_attn_mma(const float* q, const void* k_pages, const void* v_pages, const int* page_table, int page_size,
                     const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D, int DV, int chunk,
-                    float scale, SeqPos pos, cudaStream_t s) {
+                    float scale, SeqPos pos, cudaStream_t s, const float* sink, int ld_v) {
     static SmemAttrOnce once82, once81, once1;
     const int Dp = (D + 15) / 16 * 16;
     // 16-byte copies need every K and V row (and the output-channel slice) to start on a 16-byte boundary
-    const bool vec8 = (D % 8) == 0 && (DV % 8) == 0 && ((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0;
+    const bool vec8 = (D % 8) == 0 && (DV % 8) == 0 && (ld_v % 8) == 0 && ((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0;
     // two groups of warps (two key tiles per step) when four tiles of K and V fit beside Q; the exchange area of the final
     // merge (68 floats per thread of a group, 34 KB) lies over the K and V buffers, whose V part alone is 68 KB
     const bool two = vec8 && Dp <= 128;
@@ -559,7 +565,7 @@ int launch_attn_mma(const float* q, const void* k_pages, const void* v_pages, co
         if (ensure_dyn_smem(ONCE, attn_chunk_sink_mma_kernel<VEC, KHN>, (int)smem_max)) return -100;                         \
         attn_chunk_sink_mma_kernel<VEC, KHN><<<grid, 128 * KHN, smem, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table, \
                                                                            page_size, (const bf16*)gate, ld_gate, (bf16*)out, ld_out, \
-                                                                           S, Hq, G, D, DV, chunk, scale, pos);              \
+                                                                           S, Hq, G, D, DV, chunk, scale, pos, sink, ld_v);  \
     } while (0)
     if (two) LCC_ATTN_MMA(once82, true, 2);
     else if (vec8) LCC_ATTN_MMA(once81, true, 1);
@@ -588,9 +594,11 @@ int qk_norm_kv_append(int dt, const void* proj, int ld, const float* qn_w, const
 
 int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_pages, const int* page_table,
                     int page_size, const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D,
-                    int DV, int chunk, float scale, bool tensor_cores, SeqPos pos, cudaStream_t s) {
+                    int DV, int chunk, float scale, bool tensor_cores, SeqPos pos, cudaStream_t s, const float* sink, int ld_v) {
     if (!q || !k_pages || !v_pages || !page_table || !out || S < 1 || Hq < 1 || G < 1 || Hq % G || D < 1 || DV < 1)
         return -2;
+    if (ld_v <= 0) ld_v = DV;
+    if (ld_v < DV) return -2;
     // The one-CTA-per-row kernel keeps one score per key of the longest window a row of this call can have in shared memory.
     // Windows that do not fit (or whose length only the device knows, in a replayed step without chunks) go to the tiled
     // kernels, which walk the keys in tiles and take any row count.
@@ -601,12 +609,12 @@ int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_p
     if (S >= kAttnTiledMin || max_keys < 0 || smem > 160 * 1024 || force_tiled) {
         if (dt == DT_BF16 && tensor_cores && D <= kAttnMmaMaxDim)
             return launch_attn_mma(q, k_pages, v_pages, page_table, page_size, gate, ld_gate, out, ld_out, S, Hq, G, D, DV, chunk,
-                                   scale, pos, s);
+                                   scale, pos, s, sink, ld_v);
         if (dt == DT_F32)
             return launch_attn_tiled<float>(q, k_pages, v_pages, page_table, page_size, gate, ld_gate, out, ld_out, S, Hq, G, D, DV,
-                                            chunk, scale, pos, s);
+                                            chunk, scale, pos, s, sink, ld_v);
         return launch_attn_tiled<bf16>(q, k_pages, v_pages, page_table, page_size, gate, ld_gate, out, ld_out, S, Hq, G, D, DV, chunk,
-                                       scale, pos, s);
+                                       scale, pos, s, sink, ld_v);
     }
     dim3 grid(S, Hq);
     count_launch();
@@ -614,12 +622,12 @@ int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_p
         if (smem > 48 * 1024) cudaFuncSetAttribute(attn_chunk_sink_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attn_chunk_sink_kernel<float><<<grid, 128, smem, s>>>(q, (const float*)k_pages, (const float*)v_pages, page_table,
                                                               page_size, (const float*)gate, ld_gate, (float*)out, ld_out, S, Hq,
-                                                              G, D, DV, chunk, scale, pos);
+                                                              G, D, DV, chunk, scale, pos, sink, ld_v);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attn_chunk_sink_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attn_chunk_sink_kernel<bf16><<<grid, 128, smem, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table,
                                                              page_size, (const bf16*)gate, ld_gate, (bf16*)out, ld_out, S, Hq, G,
-                                                             D, DV, chunk, scale, pos);
+                                                             D, DV, chunk, scale, pos, sink, ld_v);
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }

@@ -18,15 +18,37 @@ template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = _
 
 constexpr int BM = 64, BN = 64, BK = 16;
 
+// One of several independent problems per blockIdx.z (plain calls: one group, no lists). With row_off the group's rows are
+// row_off[z] .. row_off[z+1]-1 of C and of the row list a_rows (or of A itself).
+struct Grp {
+    int64_t a_stride, w_stride, c_stride;
+    const int* row_off;
+    const int* a_rows;
+    int act;
+};
+__device__ __forceinline__ float act_of(float v, int act) {
+    if (act == ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
+    return v;
+}
+
 // 64 x 64 output tile per CTA, 256 threads x (4 x 4) accumulators, k-slices of 16 staged in shared memory as fp32.
 template <typename T, typename TC>
 __global__ void __launch_bounds__(256) linear_tile_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int ldw,
                                                           const float* __restrict__ bias, TC* __restrict__ C, int ldc, int M,
-                                                          int N, int K) {
+                                                          int N, int K, Grp g) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    int row0 = 0;
+    if (g.row_off) {
+        row0 = g.row_off[blockIdx.z];
+        M = g.row_off[blockIdx.z + 1] - row0;
+        if (m0 >= M) return;
+    }
+    A += blockIdx.z * g.a_stride; W += blockIdx.z * g.w_stride; C += blockIdx.z * g.c_stride + (size_t)row0 * ldc;
+    const int* arow = g.a_rows ? g.a_rows + row0 : nullptr;
+    if (!arow) A += (size_t)row0 * lda;
     const int tm = (tid / 16) * 4, tn = (tid % 16) * 4;
     float acc[4][4] = {};
     for (int k0 = 0; k0 < K; k0 += BK) {
@@ -35,7 +57,7 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(const T* __restrict__ 
         for (int i = 0; i < 4; ++i) {
             const int e = tid + i * 256, r = e / BK, k = e % BK;
             const int gm = m0 + r, gn = n0 + r, gk = k0 + k;
-            As[k][r] = (gm < M && gk < K) ? ldf(A + (size_t)gm * lda + gk) : 0.f;
+            As[k][r] = (gm < M && gk < K) ? ldf(A + (size_t)(arow ? arow[gm] : gm) * lda + gk) : 0.f;
             Ws[k][r] = (gn < N && gk < K) ? ldf(W + (size_t)gn * ldw + gk) : 0.f;
         }
         __syncthreads();
@@ -58,7 +80,7 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(const T* __restrict__ 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int gn = n0 + tn + j;
-            if (gn < N) stf(C + (size_t)gm * ldc + gn, acc[i][j] + (bias ? bias[gn] : 0.f));
+            if (gn < N) stf(C + (size_t)gm * ldc + gn, act_of(acc[i][j] + (bias ? bias[gn] : 0.f), g.act));
         }
     }
 }
@@ -87,11 +109,29 @@ template <> struct Vec16<float> {
 
 template <typename T, typename TC, bool VEC, int WR>
 __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int ldw,
-                                                          const float* __restrict__ bias, TC* __restrict__ C, int ldc, int M,
-                                                          int N, int K) {
+                                                          const float* __restrict__ bias, TC* __restrict__ C, int ldc, int M_all,
+                                                          int N, int K, Grp g) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = (blockIdx.x * (blockDim.x >> 5) + warp) * WR;
     if (n0 >= N) return;
+    int row0 = 0;
+    if (g.row_off) {
+        row0 = g.row_off[blockIdx.y];
+        M_all = g.row_off[blockIdx.y + 1] - row0;
+    }
+    const T* A0 = A + blockIdx.y * g.a_stride;
+    W += blockIdx.y * g.w_stride;
+    TC* C0 = C + blockIdx.y * g.c_stride + (size_t)row0 * ldc;
+    const int* arow = g.a_rows ? g.a_rows + row0 : nullptr;
+    if (!arow) A0 += (size_t)row0 * lda;
+    // a group with more than kRowsMax rows walks them in blocks (the weights come from L2 after the first block); a row's
+    // sum is the same whatever block it falls into
+    for (int mb = 0; mb < M_all; mb += kRowsMax) {
+    const int M = min(kRowsMax, M_all - mb);
+    const T* arp[kRowsMax];
+#pragma unroll
+    for (int m = 0; m < kRowsMax; ++m) arp[m] = A0 + (size_t)(m < M ? (arow ? arow[mb + m] : mb + m) : 0) * lda;
+    C = C0 + (size_t)mb * ldc;
     float acc[WR][kRowsMax];
 #pragma unroll
     for (int r = 0; r < WR; ++r)
@@ -121,7 +161,7 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ 
                 for (int m = 0; m < kRowsMax; ++m) {
                     if (m < M) {
                         float av[V];
-                        Vec16<T>::unpack(__ldg(reinterpret_cast<const uint4*>(A + (size_t)m * lda + k)), av);
+                        Vec16<T>::unpack(__ldg(reinterpret_cast<const uint4*>(arp[m] + k)), av);
 #pragma unroll
                         for (int r = 0; r < WR; ++r)
 #pragma unroll
@@ -137,7 +177,7 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ 
                 const float wv = ldf(W + (size_t)min(n0 + r, N - 1) * ldw + k);
 #pragma unroll
                 for (int m = 0; m < kRowsMax; ++m)
-                    if (m < M) acc[r][m] = fmaf(ldf(A + (size_t)m * lda + k), wv, acc[r][m]);
+                    if (m < M) acc[r][m] = fmaf(ldf(arp[m] + k), wv, acc[r][m]);
             }
         }
     }
@@ -148,22 +188,25 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ 
         for (int m = 0; m < kRowsMax; ++m) {
             if (m < M) {
                 const float v = warp_sum(acc[r][m]);
-                if (lane == 0 && n < N) stf(C + (size_t)m * ldc + n, v + (bias ? bias[n] : 0.f));
+                if (lane == 0 && n < N) stf(C + (size_t)m * ldc + n, act_of(v + (bias ? bias[n] : 0.f), g.act));
             }
         }
+    }
     }
 }
 
 template <typename T, typename TC>
 int launch_linear(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N, int K,
-                  cudaStream_t s) {
-    if (M <= kRowsMax) {
+                  cudaStream_t s, int groups = 1, Grp g = Grp{0, 0, 0, nullptr, nullptr, ACT_NONE}, int M_total = 0) {
+    // lists: the row kernel while all groups together have few rows (a decode step routes `top` rows per sequence)
+    if (g.row_off ? M_total <= 8 * kRowsMax : M <= kRowsMax) {
         constexpr int V = Vec16<T>::N;
-        const bool vec = (K % V) == 0 && (lda % V) == 0 && (ldw % V) == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0;
+        const bool vec = (K % V) == 0 && (lda % V) == 0 && (ldw % V) == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0 &&
+                         (g.a_stride % V) == 0 && (g.w_stride % V) == 0;
         count_launch();
 #define LCC_ROWS(VECB, WRN, WARPS)                                                                                         \
-    linear_rows_kernel<T, TC, VECB, WRN><<<(N + WARPS * WRN - 1) / (WARPS * WRN), WARPS * 32, 0, s>>>((const T*)A, lda, (const T*)W, \
-                                                                                                      ldw, bias, (TC*)C, ldc, M, N, K)
+    linear_rows_kernel<T, TC, VECB, WRN><<<dim3((N + WARPS * WRN - 1) / (WARPS * WRN), groups), WARPS * 32, 0, s>>>(            \
+        (const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K, g)
         if (N >= 8192) {
             if (vec) LCC_ROWS(true, 2, 8); else LCC_ROWS(false, 2, 8);
         } else {
@@ -171,9 +214,9 @@ int launch_linear(const void* A, int lda, const void* W, int ldw, const float* b
         }
 #undef LCC_ROWS
     } else {
-        dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+        dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, groups);
         count_launch();
-        linear_tile_kernel<T, TC><<<grid, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K);
+        linear_tile_kernel<T, TC><<<grid, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K, g);
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
@@ -186,6 +229,17 @@ int linear_any(int dt, const void* A, int lda, const void* W, int ldw, const flo
     if (dt == DT_F32) return launch_linear<float, float>(A, lda, W, ldw, bias, C, ldc, M, N, K, s);
     if (c_f32) return launch_linear<bf16, float>(A, lda, W, ldw, bias, C, ldc, M, N, K, s);
     return launch_linear<bf16, bf16>(A, lda, W, ldw, bias, C, ldc, M, N, K, s);
+}
+
+int linear_grouped(const GroupedLinear& q, cudaStream_t s) {
+    if (!q.A || !q.W || !q.C || q.groups < 1 || q.groups > 65535 || q.M < 1 || q.N < 1 || q.K < 1 || q.lda < q.K || q.ldw < q.K ||
+        q.ldc < q.N || (q.a_rows && !q.row_off))
+        return -2;
+    const Grp g{q.a_stride, q.w_stride, q.c_stride, q.row_off, q.a_rows, q.act};
+    const int mt = q.row_off ? (q.M_total > 0 ? q.M_total : q.M * q.groups) : 0;
+    if (q.dt == DT_F32) return launch_linear<float, float>(q.A, q.lda, q.W, q.ldw, nullptr, q.C, q.ldc, q.M, q.N, q.K, s, q.groups, g, mt);
+    if (q.c_f32) return launch_linear<bf16, float>(q.A, q.lda, q.W, q.ldw, nullptr, q.C, q.ldc, q.M, q.N, q.K, s, q.groups, g, mt);
+    return launch_linear<bf16, bf16>(q.A, q.lda, q.W, q.ldw, nullptr, q.C, q.ldc, q.M, q.N, q.K, s, q.groups, g, mt);
 }
 
 }  // namespace lcc

@@ -1,0 +1,130 @@
+// Mixture-of-experts routing: a sigmoid router with a choice-only correction, the expert-sorted row lists that the
+// grouped linear kernels walk, and the weighted combine. Router scores, weights and gates are fp32.
+#include <math.h>
+
+#include "common.cuh"
+#include "launch.h"
+#include "seqmix.h"
+
+namespace lcc {
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+
+// One warp per row. Lane l holds experts l, l + 32, ...; `top` rounds of a warp-wide arg-max (the lower index wins a tie)
+// pick the experts in descending order of choice score. The arrival number inside an expert comes from an atomic
+// counter: it decides only where the row sits in the expert's list, never a value.
+constexpr int kMaxExpertsPerLane = 16;   // experts <= 512
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ correction,
+                                                        int E, int top, float scale, int* __restrict__ sel,
+                                                        float* __restrict__ weight, float* __restrict__ shared_gate,
+                                                        int* __restrict__ counts, int* __restrict__ rank, int S) {
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= S) return;
+    const float* z = logits + (size_t)r * ld;
+    float sc[kMaxExpertsPerLane], ch[kMaxExpertsPerLane];
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+        const int e = lane + 32 * i;
+        sc[i] = e < E ? sigmoid_f(z[e]) : 0.f;
+        ch[i] = e < E ? sc[i] + correction[e] : -INFINITY;
+    }
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY, bs = 0.f;
+        int be = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+            const int e = lane + 32 * i;
+            if (e < E && ch[i] > best) { best = ch[i]; be = e; bs = sc[i]; }   // ascending e: the first of equals stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o), os = __shfl_xor_sync(0xffffffffu, bs, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; bs = os; }
+        }
+#pragma unroll
+        for (int i = 0; i < kMaxExpertsPerLane; ++i)
+            if (lane + 32 * i == be) ch[i] = -INFINITY;
+        if (lane == 0) {
+            sel[(size_t)r * top + k] = be;
+            weight[(size_t)r * top + k] = bs * scale;
+            rank[(size_t)r * top + k] = atomicAdd(counts + be, 1);
+        }
+    }
+    if (shared_gate && lane == 0) shared_gate[r] = sigmoid_f(z[E]);
+}
+
+__global__ void moe_index_kernel(const int* __restrict__ sel, const int* __restrict__ rank, const int* __restrict__ counts, int E,
+                                 int top, int* __restrict__ row_off, int* __restrict__ pos, int* __restrict__ src_row, int S) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i <= E) {
+        int o = 0;
+        for (int e = 0; e < i; ++e) o += counts[e];
+        row_off[i] = o;
+    }
+    if (i >= S * top) return;
+    const int e = sel[i];
+    int o = 0;
+    for (int j = 0; j < e; ++j) o += counts[j];
+    const int p = o + rank[i];
+    pos[i] = p;
+    src_row[p] = i / top;
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ eo, int ld_eo, const int* __restrict__ pos, const float* __restrict__ weight,
+                                   int top, const T* __restrict__ so, int ld_so, const float* __restrict__ shared_gate,
+                                   T* __restrict__ out, int ld_out, int W) {
+    const int r = blockIdx.x;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k)
+            acc = fmaf(weight[(size_t)r * top + k], ldf(eo + (size_t)pos[(size_t)r * top + k] * ld_eo + c), acc);
+        if (so) acc = fmaf(shared_gate[r], ldf(so + (size_t)r * ld_so + c), acc);
+        stf(out + (size_t)r * ld_out + c, acc);
+    }
+}
+
+}  // namespace
+
+int moe_route(const float* logits, int ld, const float* correction, int E, int top, float scale, int* sel, float* weight,
+              float* shared_gate, int* counts, int* rank, int S, cudaStream_t s) {
+    if (!logits || !correction || !sel || !weight || !counts || !rank || S < 1 || E < 1 || E > 32 * kMaxExpertsPerLane || top < 1 ||
+        top > E || ld < E + (shared_gate ? 1 : 0))
+        return -2;
+    count_launch();
+    moe_route_kernel<<<(S + 3) / 4, 128, 0, s>>>(logits, ld, correction, E, top, scale, sel, weight, shared_gate, counts, rank, S);
+    return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+int moe_index(const int* sel, const int* rank, const int* counts, int E, int top, int* row_off, int* pos, int* src_row, int S,
+              cudaStream_t s) {
+    if (!sel || !rank || !counts || !row_off || !pos || !src_row || S < 1 || E < 1 || top < 1) return -2;
+    const int n = S * top > E + 1 ? S * top : E + 1;
+    count_launch();
+    moe_index_kernel<<<(n + 255) / 256, 256, 0, s>>>(sel, rank, counts, E, top, row_off, pos, src_row, S);
+    return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+int moe_combine(int dt, const void* eo, int ld_eo, const int* pos, const float* weight, int top, const void* so, int ld_so,
+                const float* shared_gate, void* out, int ld_out, int S, int W, cudaStream_t s) {
+    if (!eo || !pos || !weight || !out || S < 1 || W < 1 || top < 1 || (so && !shared_gate)) return -2;
+    count_launch();
+    if (dt == DT_F32)
+        moe_combine_kernel<float><<<S, 256, 0, s>>>((const float*)eo, ld_eo, pos, weight, top, (const float*)so, ld_so, shared_gate,
+                                                    (float*)out, ld_out, W);
+    else
+        moe_combine_kernel<bf16><<<S, 256, 0, s>>>((const bf16*)eo, ld_eo, pos, weight, top, (const bf16*)so, ld_so, shared_gate,
+                                                   (bf16*)out, ld_out, W);
+    return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+}  // namespace lcc

@@ -23,18 +23,21 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); 
 template <typename T>
 __global__ void embed_sinusoid_kernel(const int64_t* __restrict__ ids, const int* __restrict__ seq_len, const T* __restrict__ table,
                                       int64_t vocab, float scale, const float* __restrict__ inv_freq, float* __restrict__ x32,
-                                      T* __restrict__ xa, int S, int W, SeqPos pos) {
+                                      T* __restrict__ xa, int S, int W, SeqPos pos, int copies) {
     if (seq_done(pos)) return;
     const int r = blockIdx.x;
     const int64_t id = seq_len ? ids[*seq_len - S + r] : ids[r];
     const float p = (float)(seq_past(pos, S) + r);
     const bool ok = id >= 0 && id < vocab;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float ang = p * inv_freq[c >> 1];
-        const float pe = (c & 1) ? cosf(ang) : sinf(ang);
+        float pe = 0.f;
+        if (inv_freq) {
+            const float ang = p * inv_freq[c >> 1];
+            pe = (c & 1) ? cosf(ang) : sinf(ang);
+        }
         const float v = (ok ? ldf(table + (size_t)id * W + c) * scale : 0.f) + pe;
-        x32[(size_t)r * W + c] = v;
-        stf(xa + (size_t)r * W + c, v);
+        for (int k = 0; k < copies; ++k) x32[((size_t)r * copies + k) * W + c] = v;
+        if (xa) stf(xa + (size_t)r * W + c, v);
     }
 }
 
@@ -205,6 +208,15 @@ __global__ void __launch_bounds__(256) gather_rmsnorm_kernel(const float* __rest
     for (int c = threadIdx.x; c < W; c += blockDim.x) stf(out + (size_t)i * W + c, x[c] * rn * w[c]);
 }
 
+template <typename T>
+__global__ void relu_squared_kernel(const T* __restrict__ in, int ld_in, T* __restrict__ out, int ld_out, int S, int n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)S * n) return;
+    const int r = (int)(i / n), c = (int)(i % n);
+    const float z = fmaxf(ldf(in + (size_t)r * ld_in + c), 0.f);
+    stf(out + (size_t)r * ld_out + c, z * z);
+}
+
 __global__ void softcap_kernel(float* __restrict__ x, int64_t n, float cap, float inv_cap) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] = cap * tanhf(x[i] * inv_cap);
@@ -215,13 +227,13 @@ inline int done() { return cudaGetLastError() == cudaSuccess ? 0 : -100; }
 }  // namespace
 
 int embed_sinusoid(int dt, const int64_t* ids, const int* seq_len, const void* table, int64_t vocab, float scale,
-                   const float* inv_freq, float* x32, void* xa, int S, int W, SeqPos pos, cudaStream_t s) {
-    if (!ids || !table || !inv_freq || !x32 || !xa || S < 1 || W < 1) return -2;
+                   const float* inv_freq, float* x32, void* xa, int S, int W, SeqPos pos, cudaStream_t s, int copies) {
+    if (!ids || !table || !x32 || S < 1 || W < 1 || copies < 1) return -2;
     count_launch();
     if (dt == DT_F32)
-        embed_sinusoid_kernel<float><<<S, 256, 0, s>>>(ids, seq_len, (const float*)table, vocab, scale, inv_freq, x32, (float*)xa, S, W, pos);
+        embed_sinusoid_kernel<float><<<S, 256, 0, s>>>(ids, seq_len, (const float*)table, vocab, scale, inv_freq, x32, (float*)xa, S, W, pos, copies);
     else
-        embed_sinusoid_kernel<bf16><<<S, 256, 0, s>>>(ids, seq_len, (const bf16*)table, vocab, scale, inv_freq, x32, (bf16*)xa, S, W, pos);
+        embed_sinusoid_kernel<bf16><<<S, 256, 0, s>>>(ids, seq_len, (const bf16*)table, vocab, scale, inv_freq, x32, (bf16*)xa, S, W, pos, copies);
     return done();
 }
 
@@ -284,6 +296,17 @@ int glu_gelu_tanh(int dt, const void* gu, int ld, void* out, int ld_out, int S, 
         glu_gelu_tanh_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const float*)gu, ld, (float*)out, ld_out, S, F);
     else
         glu_gelu_tanh_kernel<bf16><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const bf16*)gu, ld, (bf16*)out, ld_out, S, F);
+    return done();
+}
+
+int relu_squared(int dt, const void* in, int ld_in, void* out, int ld_out, int S, int n, cudaStream_t s) {
+    if (!in || !out || S < 1 || n < 1) return -2;
+    const int64_t tot = (int64_t)S * n;
+    count_launch();
+    if (dt == DT_F32)
+        relu_squared_kernel<float><<<(unsigned)((tot + 255) / 256), 256, 0, s>>>((const float*)in, ld_in, (float*)out, ld_out, S, n);
+    else
+        relu_squared_kernel<bf16><<<(unsigned)((tot + 255) / 256), 256, 0, s>>>((const bf16*)in, ld_in, (bf16*)out, ld_out, S, n);
     return done();
 }
 

@@ -32,6 +32,9 @@ struct Dims {
     int inner, conv_ch, s_proj;          // SSD
     int l_nq, l_nk, l_nv, l_proj, l_o;   // left
     int r_nk, r_nv, r_proj;              // right
+    int t_nk, t_nv, t_proj, t_pack;      // retention: q and k columns, v columns, projection rows, fp32 pack [q | k | v]
+    int a_nq, a_kv, a_kd, a_proj, a_gate, a_lat, a_o;   // latent attention: query columns, latent + key part, cache row, projection rows,
+                                                        // gate column, absorbed-output columns, value columns
 };
 Dims dims_of(const lcc_seq_layer& L) {
     Dims z{};
@@ -45,6 +48,18 @@ Dims dims_of(const lcc_seq_layer& L) {
         z.l_o = L.l_heads * L.l_vdim;
         z.r_nk = L.r_heads * L.r_dim; z.r_nv = L.r_heads * L.r_vdim;
         z.r_proj = 2 * z.r_nk + 2 * z.r_nv + L.r_rank;
+    } else if (L.type == LCC_MIX_RETENTION) {
+        z.t_nk = L.t_heads * L.t_dim; z.t_nv = L.t_heads * L.t_vdim;
+        z.t_proj = 2 * z.t_nk + 2 * z.t_nv;
+        z.t_pack = 2 * z.t_nk + z.t_nv;
+    } else if (L.type == LCC_MIX_LATENT) {
+        z.a_nq = L.a_heads * (L.a_dim + L.a_rot_dim);
+        z.a_kd = L.a_rank + L.a_rot_dim;
+        z.a_kv = L.a_kv_from >= 0 ? 0 : z.a_kd;
+        z.a_gate = z.a_nq + z.a_kv;
+        z.a_proj = z.a_gate + L.a_heads;
+        z.a_lat = L.a_heads * L.a_rank;
+        z.a_o = L.a_heads * L.a_vdim;
     }
     return z;
 }
@@ -54,8 +69,9 @@ Dims dims_of(const lcc_seq_layer& L) {
 inline int ld8(int n) { return (n + 7) / 8 * 8; }
 
 struct WsLayout {
-    size_t x32, xa, proj, proj2, mid, mid2, y32, q32, f1, f2, o1, o2, xf, scan, scan_floats, total;
+    size_t x32, xa, proj, proj2, mid, mid2, y32, q32, f1, f2, o1, o2, xf, scan, scan_floats, xsum, moe_f, moe_i, total;
     int w_proj, w_proj2, w_mid, w_y, w_q, w_f;
+    int moe_e, moe_top;   // largest expert count and top-k of any layer (0: no routed feed-forward)
 };
 
 WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
@@ -64,25 +80,43 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     const size_t nt = NT > 0 ? NT : 1, nw = NW > 0 ? NW : 1;
     int wp = 8, wp2 = 8, wm = 8, wy = 8, wq = 8, wf = 8;
     size_t scan_floats = 0;
+    int moe_e = 0, moe_top = 0;
     for (const lcc_seq_layer& l : m->layers) {
         const Dims z = dims_of(l);
         if (l.type == LCC_MIX_SSD) {
             wp = std::max(wp, ld8(z.s_proj)); wm = std::max(wm, ld8(std::max(z.conv_ch, z.inner)));
             wy = std::max(wy, z.inner); wf = std::max(wf, l.s_heads);
             scan_floats = std::max(scan_floats, lcc::gated_scan_ws_floats(NT, l.s_heads, l.s_state, l.s_vdim));
-        } else {
+        } else if (l.type == LCC_MIX_PARALLEL) {
             wp = std::max(wp, ld8(std::max(z.l_proj, z.r_proj))); wp2 = std::max(wp2, ld8(z.r_nk));
             wm = std::max(wm, ld8(std::max(z.l_o, z.r_nv)));
             wy = std::max(wy, z.r_nv); wq = std::max(wq, z.l_nq); wf = std::max(wf, z.r_nk);
             scan_floats = std::max(scan_floats, lcc::gated_scan_ws_floats(NT, l.r_heads, l.r_dim, l.r_vdim));
+        } else if (l.type == LCC_MIX_RETENTION) {
+            wp = std::max(wp, ld8(z.t_proj)); wm = std::max(wm, ld8(z.t_nv));
+            wy = std::max(wy, z.t_nv); wq = std::max(wq, z.t_pack); wf = std::max(wf, l.t_heads);
+            scan_floats = std::max(scan_floats, lcc::gated_scan_ws_floats(NT, l.t_heads, l.t_dim, l.t_vdim));
+        } else if (l.type == LCC_MIX_LATENT) {
+            wp = std::max(wp, ld8(z.a_proj)); wm = std::max(wm, ld8(std::max(z.a_lat, z.a_o)));
+            wq = std::max(wq, l.a_heads * z.a_kd);
         }
-        if (l.ff > 0) { wp = std::max(wp, ld8(2 * l.ff)); wm = std::max(wm, ld8(l.ff)); }
+        if (l.ff_kind == LCC_FF_MOE) {
+            // per row: `top` expert hidden rows in proj, `top` expert output rows in mid, the shared hidden row in mid2
+            wp = std::max(wp, l.e_top * ld8(l.e_ff)); wm = std::max(wm, std::max(l.e_top * ld8(m->d.width), ld8(l.e_shared_ff)));
+            moe_e = std::max(moe_e, l.e_experts); moe_top = std::max(moe_top, l.e_top);
+        } else if (l.ff > 0) { wp = std::max(wp, ld8(2 * l.ff)); wm = std::max(wm, ld8(l.ff)); }
     }
+    L.moe_e = moe_e; L.moe_top = moe_top;
     L.w_proj = wp; L.w_proj2 = wp2; L.w_mid = wm; L.w_y = wy; L.w_q = wq; L.w_f = wf;
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes); return o; };
     const int W = m->d.width;
-    L.x32 = take(nt * W * 4);
+    L.x32 = take(nt * W * 4 * (m->d.block == LCC_BLOCK_PRENORM_HC ? m->d.streams : 1));
+    L.xsum = take(m->d.block == LCC_BLOCK_PRENORM_HC ? nt * W * 4 : 0);
+    // routed feed-forward: fp32 [logits: E+1 | weights: top | shared gate: 1] per row; int32 [sel, rank, pos: top each |
+    // src_row: top] per row, then [counts: E | row_off: E+1]
+    L.moe_f = take(moe_e ? nt * (size_t)(moe_e + 2 + moe_top) * 4 : 0);
+    L.moe_i = take(moe_e ? (nt * (size_t)(4 * moe_top) + 2 * moe_e + 1) * 4 : 0);
     L.xa = take(nt * ld8(W) * es);
     L.proj = take(nt * wp * es);
     L.proj2 = take(nt * wp2 * es);
@@ -132,10 +166,23 @@ lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc
     auto fail = [&](const char* msg) -> lcc_seq_model* { snprintf(ctx->err, sizeof(ctx->err), "lcc_seq_model_create: %s", msg); return nullptr; };
     if (desc->width < 1 || desc->vocab < 1 || desc->n_layers < 1) return fail("bad sizes");
     if (desc->dtype != LCC_DT_BF16 && desc->dtype != LCC_DT_F32) return fail("unknown storage type");
-    if (!desc->embed || !desc->inv_freq_f32 || !desc->final_norm_f32 || !desc->head) return fail("missing weights");
+    if (!desc->embed || !desc->final_norm_f32 || !desc->head) return fail("missing weights");
+    const bool hc = desc->block == LCC_BLOCK_PRENORM_HC;
+    if (desc->block != LCC_BLOCK_POSTNORM && !hc) return fail("unknown block form");
+    if (hc && (desc->streams < 1 || desc->streams > 8)) return fail("1 to 8 residual streams");
     for (int i = 0; i < desc->n_layers; ++i) {
         const lcc_seq_layer& l = desc->layers[i];
+        if (l.ff_kind == LCC_FF_MOE) {
+            if (l.e_experts < 1 || l.e_experts > 512 || l.e_top < 1 || l.e_top > l.e_experts || l.e_ff < 1 || l.e_shared_ff < 0)
+                return fail("routed feed-forward: unsupported sizes");
+            if (!l.norm2_f32 || !l.e_router || !l.e_correction_f32 || !l.e_up || !l.e_down || (l.e_shared_ff > 0 && (!l.e_shared_up || !l.e_shared_down)))
+                return fail("routed feed-forward: missing weights");
+        } else if (l.ff_kind != LCC_FF_GLU) {
+            return fail("unknown feed-forward kind");
+        }
         if (!l.norm1_f32 || (l.ff > 0 && (!l.norm2_f32 || !l.ff_in || !l.ff_out))) return fail("missing norm / feed-forward weights");
+        if (hc && (!l.hc1_f32 || ((l.ff > 0 || l.ff_kind == LCC_FF_MOE) && !l.hc2_f32))) return fail("missing stream weights");
+        if (hc && l.type == LCC_MIX_PARALLEL) return fail("the parallel mixer merges its branches in a post-norm block");
         if (l.type == LCC_MIX_SSD) {
             if (l.s_heads < 1 || l.s_vdim < 1 || l.s_state < 1 || l.s_state > 512 || l.s_groups < 1 || l.s_heads % l.s_groups ||
                 l.s_conv < 1 || l.s_conv > 8 || l.s_norm_groups < 1 || (l.s_heads * l.s_vdim) % l.s_norm_groups)
@@ -149,6 +196,24 @@ lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc
             if (!l.l_in || !l.l_in_bias_f32 || !l.l_qnorm_f32 || !l.l_knorm_f32 || !l.l_out || !l.l_branch_norm_f32 || !l.r_in ||
                 !l.r_decay_up || !l.r_decay_bias_f32 || !l.r_norm_f32 || !l.r_out || !l.r_branch_norm_f32)
                 return fail("parallel layer: missing weights");
+        } else if (l.type == LCC_MIX_RETENTION) {
+            if (l.t_heads < 1 || l.t_dim < 1 || l.t_dim > 512 || l.t_vdim < 1 || l.t_rot_dims < 0 || (l.t_rot_dims & 1) || l.t_rot_dims > l.t_dim)
+                return fail("retention layer: unsupported sizes");
+            if (!l.t_in || !l.t_log_decay_f32 || !l.t_norm_f32 || !l.t_out || (l.t_rot_dims > 0 && !l.rot_inv_freq_f32))
+                return fail("retention layer: missing weights");
+        } else if (l.type == LCC_MIX_LATENT) {
+            if (l.a_heads < 1 || l.a_dim < 1 || l.a_rot_dim < 2 || (l.a_rot_dim & 1) || l.a_vdim < 1 || l.a_rank < 1)
+                return fail("latent attention layer: unsupported sizes");
+            if (l.a_kv_from >= 0) {
+                if (l.a_kv_from >= i) return fail("latent attention layer: the shared cache must belong to an earlier layer");
+                const lcc_seq_layer& o = desc->layers[l.a_kv_from];
+                if (o.type != LCC_MIX_LATENT || o.a_kv_from >= 0 || o.a_rank != l.a_rank || o.a_rot_dim != l.a_rot_dim)
+                    return fail("latent attention layer: the shared cache has another geometry");
+            } else if (!l.a_latent_norm_f32) {
+                return fail("latent attention layer: missing weights");
+            }
+            if (!l.a_in || !l.a_uk_t || !l.a_uv || !l.a_sink_f32 || !l.a_out || !l.rot_inv_freq_f32)
+                return fail("latent attention layer: missing weights");
         } else {
             return fail("unknown mixer type");
         }
@@ -181,6 +246,8 @@ int64_t lcc_seq_layer_state_floats(const lcc_seq_model* m, int layer) {
     const lcc_seq_layer& l = m->layers[layer];
     const Dims z = dims_of(l);
     if (l.type == LCC_MIX_SSD) return (int64_t)z.conv_ch * (l.s_conv - 1) + (int64_t)l.s_heads * l.s_vdim * l.s_state;
+    if (l.type == LCC_MIX_RETENTION) return (int64_t)l.t_heads * l.t_vdim * l.t_dim;
+    if (l.type == LCC_MIX_LATENT) return 0;
     return (int64_t)l.r_heads * l.r_vdim * l.r_dim;
 }
 
@@ -208,6 +275,18 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
     float* f1 = (float*)(ws + L.f1); float* f2 = (float*)(ws + L.f2);
     uint8_t* o1 = ws + L.o1; uint8_t* o2 = ws + L.o2; uint8_t* xf = ws + L.xf;
     float* scan_ws = L.scan_floats ? (float*)(ws + L.scan) : nullptr;
+    const bool hc = d.block == LCC_BLOCK_PRENORM_HC;
+    const int NS = hc ? d.streams : 1;
+    float* xsum = (float*)(ws + L.xsum);
+    // pre-norm blocks: the sublayer output that the next boundary kernel folds into the streams
+    const float* pend_hc = nullptr;
+    // boundary between sublayers of a pre-norm block: fold the finished sublayer's output (o1) into the streams, read and
+    // norm for the next one (next_hc / next_w; null at the end of the model), optionally emit the sum of the streams
+    auto boundary = [&](const float* next_hc, const float* next_w, float* sum_out) -> int {
+        const int rc = lcc::hyper_boundary(dt, x32, NS, pend_hc ? ws + L.o1 : nullptr, W, pend_hc, next_hc, next_w, d.eps, xa, sum_out, T, W, s);
+        pend_hc = nullptr;
+        return rc;
+    };
     auto pos_of = [&](const lcc_seq_entry& e) {
         lcc::SeqPos p{e.past, nullptr, nullptr};
         if (e.scalars) { p.kv_len = e.scalars + LCC_SC_KV_LEN; p.finished = e.scalars + LCC_SC_FINISHED; }
@@ -219,14 +298,93 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
         for (int e = 0; e < n_entries; ++e) {
             const lcc_seq_entry& en = entries[e];
             STEP(lcc::embed_sinusoid(dt, en.ids, en.scalars ? en.scalars + LCC_SC_SEQ_LEN : nullptr, d.embed, d.vocab, d.embed_scale,
-                                     d.inv_freq_f32, x32 + (size_t)r0 * W, xa + (size_t)r0 * W * es, en.n_new, W, pos_of(en), s), "embedding");
+                                     d.inv_freq_f32, x32 + (size_t)r0 * W * NS, hc ? nullptr : xa + (size_t)r0 * W * es, en.n_new, W,
+                                     pos_of(en), s, NS), "embedding");
             r0 += en.n_new;
         }
     }
     for (int li = 0; li < d.n_layers; ++li) {
         const lcc_seq_layer& l = m->layers[li];
         const Dims z = dims_of(l);
-        if (l.type == LCC_MIX_SSD) {
+        if (hc) STEP(boundary(l.hc1_f32, l.norm1_f32, (layer_dump && li > 0) ? layer_dump + (size_t)(li - 1) * T * W : nullptr), "stream boundary");
+        if (l.type == LCC_MIX_RETENTION) {
+            // [q | k | v | gate] -> rotary q, k (k scaled), everything that enters the recurrence packed as fp32 -> recurrence
+            // with one constant decay per head -> unit-rms heads x silu(gate) -> out-proj
+            const int ldp = ld8(z.t_proj), ldv = ld8(z.t_nv), H = l.t_heads;
+            STEP(linear(m, xa, W, l.t_in, nullptr, proj, ldp, false, T, z.t_proj, W, s), "retention in-proj");
+            int r0 = 0;
+            for (int e = 0; e < n_entries; ++e) {
+                const lcc_seq_entry& en = entries[e];
+                float* st = en.layer_state[li];
+                if (!st) LCC_FAIL(m->ctx, -2, "lcc_seq_forward: entry %d has no state for layer %d", e, li);
+                const lcc::SeqPos pos = pos_of(en);
+                float* pk = q32 + (size_t)r0 * z.t_pack;
+                const lcc::RotarySegment seg[3] = {
+                    {0, 0, H, l.t_dim, 0, l.t_rot_dims, 1.f},
+                    {z.t_nk, z.t_nk, H, l.t_dim, 0, l.t_rot_dims, 1.f / sqrtf((float)l.t_dim)},
+                    {2 * z.t_nk, 2 * z.t_nk, H, l.t_vdim, 0, 0, 1.f}};
+                STEP(lcc::rotary_pack_f32(dt, proj + (size_t)r0 * ldp * es, ldp, pk, z.t_pack, seg, 3, l.rot_inv_freq_f32, l.rot_mag,
+                                          l.t_log_decay_f32, f1 + (size_t)r0 * H, H, en.n_new, pos, s), "rotary positions");
+                lcc::ScanArgs a{};
+                a.dt = LCC_DT_F32;      // the packed operands are fp32 in both storage types
+                a.k = pk + z.t_nk; a.ld_k = z.t_pack;
+                a.c = pk; a.ld_c = z.t_pack;
+                a.u = pk + 2 * z.t_nk; a.ld_u = z.t_pack;
+                a.a = f1 + (size_t)r0 * H; a.vec_decay = 0;
+                a.sc = nullptr; a.skip = nullptr; a.cs = 1.f;
+                a.state = st;
+                a.y = y32 + (size_t)r0 * z.t_nv; a.ld_y = z.t_nv;
+                a.S = en.n_new; a.heads = H; a.heads_per_group = 1; a.N = l.t_dim; a.P = l.t_vdim;
+                a.ws = scan_ws; a.ws_floats = L.scan_floats;
+                STEP(lcc::gated_scan(a, pos, s), "retention recurrence");
+                r0 += en.n_new;
+            }
+            STEP(lcc::gated_group_norm(dt, y32, z.t_nv, proj + (size_t)(2 * z.t_nk + z.t_nv) * es, ldp, l.t_norm_f32, l.t_vdim, mid2, ldv, T,
+                                       z.t_nv, l.t_vdim, 0, d.eps, s), "head norm + gate");
+            STEP(linear(m, mid2, ldv, l.t_out, nullptr, o1, W, false, T, W, z.t_nv, s), "retention out-proj");
+        } else if (l.type == LCC_MIX_LATENT) {
+            // [q | latent, key part | gate] -> cache append + rotary query part -> unrotated query part absorbed through
+            // W_uk^T per head -> attention over the cache rows (one key/value head, values = the latent channels) ->
+            // per-head W_uv -> out-proj
+            const int ldp = ld8(z.a_proj), ldl = ld8(z.a_lat), ldo = ld8(z.a_o), H = l.a_heads, QH = l.a_dim + l.a_rot_dim;
+            const int src = l.a_kv_from >= 0 ? l.a_kv_from : li;
+            STEP(linear(m, xa, W, l.a_in, nullptr, proj, ldp, false, T, z.a_proj, W, s), "latent attention in-proj");
+            int r0 = 0;
+            for (int e = 0; e < n_entries; ++e) {
+                const lcc_seq_entry& en = entries[e];
+                if (!en.k_pages || !en.k_pages[src] || !en.page_table)
+                    LCC_FAIL(m->ctx, -2, "lcc_seq_forward: entry %d has no pages for layer %d", e, src);
+                STEP(lcc::latent_kv_append(dt, proj + (size_t)r0 * ldp * es, ldp, l.a_kv_from < 0, l.a_latent_norm_f32, d.eps,
+                                           l.rot_inv_freq_f32, l.rot_mag, q32 + (size_t)r0 * H * z.a_kd, en.k_pages[src], en.page_table,
+                                           page_size, en.n_new, H, l.a_dim, l.a_rot_dim, l.a_rank, pos_of(en), s), "latent cache append");
+                r0 += en.n_new;
+            }
+            {
+                lcc::GroupedLinear g{};
+                g.dt = dt; g.A = proj; g.lda = ldp; g.a_stride = QH;
+                g.W = l.a_uk_t; g.ldw = l.a_dim; g.w_stride = (int64_t)l.a_rank * l.a_dim;
+                g.C = q32; g.ldc = H * z.a_kd; g.c_stride = z.a_kd; g.c_f32 = true;
+                g.groups = H; g.M = T; g.N = l.a_rank; g.K = l.a_dim;
+                STEP(lcc::linear_grouped(g, s), "query absorption");
+            }
+            r0 = 0;
+            for (int e = 0; e < n_entries; ++e) {
+                const lcc_seq_entry& en = entries[e];
+                STEP(lcc::attn_chunk_sink(dt, q32 + (size_t)r0 * H * z.a_kd, en.k_pages[src], en.k_pages[src], en.page_table, page_size,
+                                          proj + ((size_t)r0 * ldp + z.a_gate) * es, ldp, mid + (size_t)r0 * ldl * es, ldl, en.n_new, H, 1,
+                                          z.a_kd, l.a_rank, 0, l.a_scale, m->use_tc, pos_of(en), s, l.a_sink_f32, z.a_kd), "latent attention");
+                r0 += en.n_new;
+            }
+            {
+                lcc::GroupedLinear g{};
+                g.dt = dt; g.A = mid; g.lda = ldl; g.a_stride = l.a_rank;
+                g.W = l.a_uv; g.ldw = l.a_rank; g.w_stride = (int64_t)l.a_vdim * l.a_rank;
+                g.C = mid2; g.ldc = ldo; g.c_stride = l.a_vdim; g.c_f32 = false;
+                g.groups = H; g.M = T; g.N = l.a_vdim; g.K = l.a_rank;
+                STEP(lcc::linear_grouped(g, s), "value up-projection");
+            }
+            STEP(linear(m, mid2, ldo, l.a_out, nullptr, o1, W, false, T, W, z.a_o, s), "latent attention out-proj");
+        } else if (l.type == LCC_MIX_SSD) {
             const int ldp = ld8(z.s_proj), ldm = ld8(z.conv_ch), GN = l.s_groups * l.s_state;
             STEP(linear(m, xa, W, l.s_in, nullptr, proj, ldp, false, T, z.s_proj, W, s), "state-space in-proj");
             STEP(lcc::ssm_step_decay(dt, proj + (size_t)(z.inner + z.conv_ch) * es, ldp, l.s_dt_bias_f32, l.s_a_log_f32, f1, f2, T,
@@ -260,7 +418,6 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             STEP(lcc::gated_group_norm(dt, y32, z.inner, proj, ldp, l.s_norm_f32, z.inner, mid2, ldi, T, z.inner,
                                        z.inner / l.s_norm_groups, 1, d.eps, s), "gated norm");
             STEP(linear(m, mid2, ldi, l.s_out, nullptr, o1, W, false, T, W, z.inner, s), "state-space out-proj");
-            STEP(lcc::postnorm_residual(dt, x32, xa, o1, W, nullptr, nullptr, 0, nullptr, l.norm1_f32, d.alpha, d.eps, T, W, s), "norm1");
         } else {
             // left: chunk-local attention with a sink
             const int ldl = ld8(z.l_proj), ldo = ld8(z.l_o);
@@ -313,20 +470,63 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             STEP(lcc::postnorm_residual(dt, x32, xa, o1, W, l.l_branch_norm_f32, o2, W, l.r_branch_norm_f32, l.norm1_f32, d.alpha, d.eps,
                                         T, W, s), "branch merge + norm1");
         }
-        if (l.ff > 0) {
+        // ---- the mixer's output is in o1 ----
+        if (hc) pend_hc = l.hc1_f32;
+        else if (l.type != LCC_MIX_PARALLEL)
+            STEP(lcc::postnorm_residual(dt, x32, xa, o1, W, nullptr, nullptr, 0, nullptr, l.norm1_f32, d.alpha, d.eps, T, W, s), "norm1");
+        const bool has_ff = l.ff > 0 || l.ff_kind == LCC_FF_MOE;
+        if (has_ff && hc) STEP(boundary(l.hc2_f32, l.norm2_f32, nullptr), "stream boundary");
+        if (l.ff_kind == LCC_FF_MOE) {
+            const int E = l.e_experts, K = l.e_top, lde = E + 1, ldh = ld8(l.e_ff), ldw8 = ld8(W), lds = ld8(l.e_shared_ff);
+            float* mf = (float*)(ws + L.moe_f);
+            float* logit = mf; float* wsel = mf + (size_t)T * lde; float* sgate = wsel + (size_t)T * K;
+            int* mi = (int*)(ws + L.moe_i);
+            int* sel = mi; int* rank = sel + (size_t)T * K; int* posn = rank + (size_t)T * K; int* src_row = posn + (size_t)T * K;
+            int* counts = src_row + (size_t)T * K; int* row_off = counts + E;
+            const bool shared = l.e_shared_ff > 0;
+            // router logits (and the shared expert's gate logit) accumulate in fp32 from the normed row
+            STEP(lcc::linear_any(dt, xa, W, l.e_router, W, nullptr, logit, lde, true, T, E + (shared ? 1 : 0), W, s), "router");
+            if (cudaMemsetAsync(counts, 0, sizeof(int) * E, s) != cudaSuccess) LCC_FAIL(m->ctx, -100, "router counters");
+            STEP(lcc::moe_route(logit, lde, l.e_correction_f32, E, K, l.e_scale, sel, wsel, shared ? sgate : nullptr, counts, rank, T, s), "expert choice");
+            STEP(lcc::moe_index(sel, rank, counts, E, K, row_off, posn, src_row, T, s), "expert row lists");
+            lcc::GroupedLinear g{};
+            g.dt = dt; g.A = xa; g.lda = W; g.a_stride = 0; g.a_rows = src_row; g.row_off = row_off; g.M_total = T * K;
+            g.W = l.e_up; g.ldw = W; g.w_stride = (int64_t)l.e_ff * W;
+            g.C = proj; g.ldc = ldh; g.c_stride = 0; g.c_f32 = false;
+            g.groups = E; g.M = T; g.N = l.e_ff; g.K = W; g.act = lcc::ACT_RELU2;
+            STEP(lcc::linear_grouped(g, s), "experts up");
+            g.A = proj; g.lda = ldh; g.a_rows = nullptr;
+            g.W = l.e_down; g.ldw = l.e_ff; g.w_stride = (int64_t)W * l.e_ff;
+            g.C = mid; g.ldc = ldw8; g.N = W; g.K = l.e_ff; g.act = lcc::ACT_NONE;
+            STEP(lcc::linear_grouped(g, s), "experts down");
+            if (shared) {
+                STEP(linear(m, xa, W, l.e_shared_up, nullptr, mid2, lds, false, T, l.e_shared_ff, W, s), "shared expert up");
+                STEP(lcc::relu_squared(dt, mid2, lds, mid2, lds, T, l.e_shared_ff, s), "shared expert activation");
+                STEP(linear(m, mid2, lds, l.e_shared_down, nullptr, o2, W, false, T, W, l.e_shared_ff, s), "shared expert down");
+            }
+            STEP(lcc::moe_combine(dt, mid, ldw8, posn, wsel, K, shared ? o2 : nullptr, W, sgate, o1, W, T, W, s), "expert combine");
+        } else if (l.ff > 0) {
             const int ldg = ld8(2 * l.ff), ldf = ld8(l.ff);
             STEP(linear(m, xa, W, l.ff_in, nullptr, proj, ldg, false, T, 2 * l.ff, W, s), "feed-forward in");
             STEP(lcc::glu_gelu_tanh(dt, proj, ldg, mid, ldf, T, l.ff, s), "gated gelu");
             STEP(linear(m, mid, ldf, l.ff_out, nullptr, o1, W, false, T, W, l.ff, s), "feed-forward out");
-            STEP(lcc::postnorm_residual(dt, x32, xa, o1, W, nullptr, nullptr, 0, nullptr, l.norm2_f32, d.alpha, d.eps, T, W, s), "norm2");
         }
-        if (layer_dump) {
+        if (has_ff) {
+            if (hc) pend_hc = l.hc2_f32;
+            else STEP(lcc::postnorm_residual(dt, x32, xa, o1, W, nullptr, nullptr, 0, nullptr, l.norm2_f32, d.alpha, d.eps, T, W, s), "norm2");
+        }
+        if (layer_dump && !hc) {
             if (cudaMemcpyAsync(layer_dump + (size_t)li * T * W, x32, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, s) != cudaSuccess)
                 LCC_FAIL(m->ctx, -100, "layer dump copy failed");
         }
     }
+    if (hc) {
+        STEP(boundary(nullptr, nullptr, xsum), "stream sum");
+        if (layer_dump && cudaMemcpyAsync(layer_dump + (size_t)(d.n_layers - 1) * T * W, xsum, (size_t)T * W * 4, cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+            LCC_FAIL(m->ctx, -100, "layer dump copy failed");
+    }
     if (n_want > 0) {
-        STEP(lcc::gather_rmsnorm(dt, x32, want_rows, d.final_norm_f32, d.eps, xf, n_want, W, s), "final norm");
+        STEP(lcc::gather_rmsnorm(dt, hc ? xsum : x32, want_rows, d.final_norm_f32, d.eps, xf, n_want, W, s), "final norm");
         STEP(lcc::linear_any(dt, xf, W, d.head, W, nullptr, logits, d.vocab, true, n_want, d.vocab, W, s), "output head");
         STEP(lcc::softcap(logits, (int64_t)n_want * d.vocab, d.logit_softcap, s), "logit soft cap");
         if (logits_copy &&

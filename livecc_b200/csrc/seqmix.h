@@ -4,6 +4,10 @@
 //   recurrent.cu    short causal convolution with carried inputs, gated linear recurrences with carried fp32 state
 //   attn_local.cu   whole-projection q/k norm + paged K/V append, chunk-local attention with a sink term
 //   rowops.cu       embedding + sinusoidal positions, post-norm residual, grouped gated RMS norm, GLU, soft cap
+//   rotary.cu       rotate-half rotary positions on slices of a projection, packed to fp32 for a recurrence
+//   attn_latent.cu  latent (low-rank) K/V cache: latent norm + shared rotary key part -> pages, rotary query part
+//   hyper.cu        pre-norm blocks on several residual streams (hyper-connections)
+//   moe.cu          sigmoid top-k router, expert row lists, weighted combine
 // Every op exists for two storage types (DT_BF16: bf16 storage, fp32 arithmetic where the model asks for it;
 // DT_F32: everything fp32). All return 0 on success, negative on invalid arguments; launches are asynchronous on `s`.
 #pragma once
@@ -29,6 +33,25 @@ struct SeqPos {
 // c_f32. Any M, N, K >= 1; leading dimensions in elements.
 int linear_any(int dt, const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, bool c_f32,
                int M, int N, int K, cudaStream_t s);
+
+// The same product for `groups` independent problems in one launch (per-head projections, routed experts). Group z reads
+// A + z * a_stride, W + z * w_stride and writes C + z * c_stride (strides in elements). Without row_off every group has M
+// rows. With row_off (device int32[groups + 1]) group z owns rows row_off[z] .. row_off[z+1]-1 of A and C, M is an upper
+// bound of any group's row count and M_total of their sum; a_rows (optional, device int32) then names the row of A that
+// feeds each of those rows (a gather), while C rows stay in list order. act: 0 none, 1 relu(x)^2 before the store.
+struct GroupedLinear {
+    int dt;
+    const void* A; int lda; int64_t a_stride;
+    const void* W; int ldw; int64_t w_stride;
+    void* C; int ldc; int64_t c_stride; bool c_f32;
+    int groups, M, N, K;
+    const int* row_off; const int* a_rows; int M_total;
+    int act;
+};
+enum { ACT_NONE = 0, ACT_RELU2 = 1 };
+int linear_grouped(const GroupedLinear& g, cudaStream_t s);
+// out[r, c] = relu(in[r, c])^2  (storage dt)
+int relu_squared(int dt, const void* in, int ld_in, void* out, int ld_out, int S, int n, cudaStream_t s);
 
 // ---- recurrent.cu -------------------------------------------------------------------------------------------------------
 // Causal per-channel convolution over `taps` inputs followed by silu. in/out: [S, C] slices (storage dt, leading
@@ -92,15 +115,67 @@ int qk_norm_kv_append(int dt, const void* proj, int ld, const float* qn_w, const
 // the same tiling with both products on the tensor cores (bf16 operands, fp32 accumulation, fp32 softmax).
 constexpr int kAttnTiledMin = 16;
 constexpr int kAttnMmaMaxDim = 256;
+// sink: fp32 [Hq] sink logits (null: 0 for every head); the sink adds exp(sink[h]) to the denominator and nothing else.
+// ld_v: elements between consecutive V rows of a (page, group); DV for V pages of their own, and the K row length when the
+// values are the first DV channels of the key rows (v_pages = k_pages), as in a latent cache.
 int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_pages, const int* page_table,
                     int page_size, const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D,
-                    int DV, int chunk, float scale, bool tensor_cores, SeqPos pos, cudaStream_t s);
+                    int DV, int chunk, float scale, bool tensor_cores, SeqPos pos, cudaStream_t s,
+                    const float* sink = nullptr, int ld_v = 0);
+
+// ---- rotary.cu ----------------------------------------------------------------------------------------------------------
+// Rotary positions in the rotate-half layout: inside a head, channel i < dims/2 of the rotated block pairs with channel
+// i + dims/2; the pair (u, v) at position p becomes (u cos a - v sin a, v cos a + u sin a) * mag, a = p * inv_freq[i]
+// (fp32 position, angle, cos and sin). A segment is `heads` heads of `dim` channels starting at column `col_in` of a row
+// of `in` (storage dt); the rotated block is channels [rot_off, rot_off + rot_dims) of each head, the rest pass; every
+// output is multiplied by `scale` and written as fp32 at column col_out of `out` with the same head layout.
+struct RotarySegment { int col_in, col_out, heads, dim, rot_off, rot_dims; float scale; };
+// Up to 4 segments of one row in one launch. fill: optional fp32 [fill_n] row that is copied to fill_out [S, fill_n] for
+// every row (per-head constants a recurrence wants per token, e.g. log decays).
+int rotary_pack_f32(int dt, const void* in, int ld_in, float* out, int ld_out, const RotarySegment* seg, int n_seg,
+                    const float* inv_freq, float mag, const float* fill, float* fill_out, int fill_n, int S, SeqPos pos,
+                    cudaStream_t s);
+
+// ---- attn_latent.cu -----------------------------------------------------------------------------------------------------
+// Rows of `proj` (storage dt) are laid out [q: H x (D + DR) | latent: R, key part: DR | ...]; has_kv = 0: no middle block.
+// With has_kv: c = rms(latent) * norm_w (fp32) and the rotated key part go to the K pages [page][1][page_size][R + DR]
+// at positions past .. past+S-1. Always: the rotated part of each head's query goes to q_out fp32 [S, H, R + DR] at
+// channels R .. R+DR-1 (channels 0 .. R-1 are left for the absorbed unrotated part: W_uk_h^T q_h).
+int latent_kv_append(int dt, const void* proj, int ld, int has_kv, const float* norm_w, float eps, const float* inv_freq,
+                     float mag, float* q_out, void* k_pages, const int* page_table, int page_size, int S, int H, int D,
+                     int DR, int R, SeqPos pos, cudaStream_t s);
+
+// ---- hyper.cu -----------------------------------------------------------------------------------------------------------
+// One boundary between two sublayers of a pre-norm block on n residual streams xs fp32 [S, n, W]:
+//   (1) if y: x_t <- sum_s mix[s * n + t] x_s + out[t] * y            (all streams at once from the old ones; y storage dt)
+//   (2) if w:  u = sum_s in[s] x_s;  xa = u / sqrt(mean(u^2) + eps) * w   (storage dt; w is the full weight)
+//   (3) if sum_out: sum_out = sum_s x_s  (fp32 [S, W])
+// prev: fp32 [in: n | out: n | mix: n*n] of the sublayer that produced y; next: the same block of the sublayer that reads xa.
+int hyper_boundary(int dt, float* xs, int n, const void* y, int ld_y, const float* prev, const float* next, const float* w,
+                   float eps, void* xa, float* sum_out, int S, int W, cudaStream_t s);
+
+// ---- moe.cu -------------------------------------------------------------------------------------------------------------
+// Router of a mixture of experts. logits fp32 [S, ld] (E expert logits, then optionally the shared expert's gate logit at
+// column E). score = sigmoid(logit); the `top` experts with the largest score + correction[e] are chosen (ties: the lower
+// index), weight = score * scale (no renormalisation). Outputs: sel int32 [S, top], weight fp32 [S, top],
+// shared_gate fp32 [S] = sigmoid(logit[E]) (when shared_gate is non-null); counts int32 [E] must be zero on entry and
+// receives the number of rows per expert; rank int32 [S, top] = the row's arrival number inside its expert.
+int moe_route(const float* logits, int ld, const float* correction, int E, int top, float scale, int* sel, float* weight,
+              float* shared_gate, int* counts, int* rank, int S, cudaStream_t s);
+// row_off int32 [E+1] = exclusive prefix sum of counts; pos[r, k] = row_off[sel] + rank = the row's place in the expert-sorted
+// list; src_row[pos] = r.
+int moe_index(const int* sel, const int* rank, const int* counts, int E, int top, int* row_off, int* pos, int* src_row, int S,
+              cudaStream_t s);
+// out[r, :] = sum_k weight[r, k] * eo[pos[r, k], :] (+ shared_gate[r] * so[r, :])   (eo, so, out: storage dt)
+int moe_combine(int dt, const void* eo, int ld_eo, const int* pos, const float* weight, int top, const void* so, int ld_so,
+                const float* shared_gate, void* out, int ld_out, int S, int W, cudaStream_t s);
 
 // ---- rowops.cu ----------------------------------------------------------------------------------------------------------
-// x[r, :] = table[id_r, :] * scale + sinusoid(past + r): entry 2i = sin(p * inv_freq[i]), 2i+1 = cos of the same.
-// ids: device int64; when seq_len is non-null, row r reads ids[*seq_len - S + r]. x32: fp32 [S, W]; xa: copy in storage dt.
+// x[r, :] = table[id_r, :] * scale + sinusoid(past + r): entry 2i = sin(p * inv_freq[i]), 2i+1 = cos of the same
+// (inv_freq null: no position term). ids: device int64; when seq_len is non-null, row r reads ids[*seq_len - S + r].
+// x32: fp32 [S, copies, W], every copy the same; xa: copy in storage dt [S, W], or null.
 int embed_sinusoid(int dt, const int64_t* ids, const int* seq_len, const void* table, int64_t vocab, float scale,
-                   const float* inv_freq, float* x32, void* xa, int S, int W, SeqPos pos, cudaStream_t s);
+                   const float* inv_freq, float* x32, void* xa, int S, int W, SeqPos pos, cudaStream_t s, int copies = 1);
 // Post-norm residual block: m = a, or (two branches) m = (rms(a) * wa + rms(b) * wb) / 2; x <- rms(alpha * x + m) * w.
 // a, b: [S, W] (storage dt); wa, wb, w: fp32 [W]; x32 updated in place, xa = copy in storage dt.
 int postnorm_residual(int dt, float* x32, void* xa, const void* a, int ld_a, const float* wa, const void* b, int ld_b,

@@ -193,6 +193,8 @@ class SeqStatePool(PageAllocator):
     * Attention layers: K pages [num_pages, kv_heads, PAGE_SIZE, dim] and V pages [num_pages, kv_heads, PAGE_SIZE, vdim]
       per layer (layers may differ in geometry; page ids are shared by all layers). A chunk-local layer never looks
       behind the start of the current chunk, so a sequence gives pages back as soon as every attention layer has left them.
+      vdim = 0: the layer keeps K pages only (a latent cache, whose values are channels of the key rows); a layer that
+      reads another layer's cache has no entry here.
     * Recurrent layers: one fp32 slot per sequence and layer (`state_floats[i]` elements, 0 for none), zeroed when a
       sequence takes it.
     attn_layers: {layer index: (kv_heads, dim, vdim, chunk)}; state_floats: per layer."""
@@ -214,10 +216,11 @@ class SeqStatePool(PageAllocator):
     def _resize_storage(self, new_total: int):
         for i, (g, d, dv, _chunk) in self.attn_layers.items():
             k = torch.zeros((new_total, g, PAGE_SIZE, d), dtype=self.dtype, device=self.device)
-            v = torch.zeros((new_total, g, PAGE_SIZE, dv), dtype=self.dtype, device=self.device)
+            v = torch.zeros((new_total, g, PAGE_SIZE, dv), dtype=self.dtype, device=self.device) if dv else None
             if self.k[i] is not None:
                 k[: self.num_pages].copy_(self.k[i])
-                v[: self.num_pages].copy_(self.v[i])
+                if v is not None:
+                    v[: self.num_pages].copy_(self.v[i])
             self.k[i], self.v[i] = k, v
 
     def keep_from(self, seq_len: int) -> int:

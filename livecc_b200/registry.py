@@ -22,6 +22,7 @@ def register(architecture: str, module: str, cls: str) -> None:
 register("Qwen2VLForConditionalGeneration", "livecc_b200.engine", "LiveCCB200ForConditionalGeneration")
 register("qwen2_vl", "livecc_b200.engine", "LiveCCB200ForConditionalGeneration")
 register("Bimopel", "livecc_b200.seq_engine", "SeqLMForCausalLM")
+register("Kedelorn", "livecc_b200.seq_engine", "SeqLMForCausalLM")
 
 
 def architectures() -> list:

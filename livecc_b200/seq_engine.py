@@ -1,5 +1,6 @@
-"""Hybrid sequence models (decoder-only language models built from state-space, gated-linear-attention and chunk-local
-attention mixers) behind the same surface as the video-language engine: `from_pretrained`, `generate`, a cache object that
+"""Hybrid sequence models (decoder-only language models built from state-space, gated-linear-attention, chunk-local
+attention, retention and latent-attention mixers, in post-norm blocks or pre-norm blocks on several residual streams, with
+dense or routed feed-forwards) behind the same surface as the video-language engine: `from_pretrained`, `generate`, a cache object that
 callers pass back, greedy token selection in the library's sampling kernel.
 
     model = SeqLMForCausalLM.from_pretrained(path, torch_dtype="bfloat16", device_map="cuda")
@@ -63,19 +64,68 @@ class SeqWeights:
         def f32(x):
             return x.to(device=device, dtype=torch.float32).contiguous()
 
+        def norm_w(name):   # layer norms whose weights are stored around zero are applied as 1 + w (summed in fp32)
+            return f32(get(name).to(torch.float32) + cfg.norm_offset) if cfg.norm_offset else f32(get(name))
+
+        def check(name, want):
+            if shape(name) != tuple(want):
+                raise ValueError(f"{name} has shape {shape(name)}, config.json implies {tuple(want)}")
+
+        def rotary(rot):
+            freq, mag = rot.frequencies()
+            return torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(device), float(mag)
+
         W = cfg.width
         self.embed = mat("embed")
         self.head = mat("head")
-        self.final_norm = f32(get("final.norm"))
+        self.final_norm = norm_w("final.norm")
         if shape("embed") != (cfg.vocab, W) or shape("head") != (cfg.vocab, W):
             raise ValueError("embed / head do not have the shape [vocab, width] of config.json")
-        i2 = torch.arange(0, W, 2, dtype=torch.float32)
-        self.inv_freq = torch.pow(torch.tensor(10000.0, dtype=torch.float32), -i2 / W).to(device)
+        self.inv_freq = None
+        if cfg.positions == "sinusoid":
+            i2 = torch.arange(0, W, 2, dtype=torch.float32)
+            self.inv_freq = torch.pow(torch.tensor(10000.0, dtype=torch.float32), -i2 / W).to(device)
+        hc = cfg.block == "prenorm_hc"
         self.layers: List[dict] = []
         for i, L in enumerate(cfg.layers):
             p = f"l{i}."
-            w = {"norm1": f32(get(p + "norm1"))}
-            if L.type == "mamba2":
+            w = {"norm1": norm_w(p + "norm1")}
+            if hc:
+                n = cfg.streams
+                for q in ("hc1", "hc2") if (L.ff or L.moe) else ("hc1",):
+                    a = p + q + "."
+                    check(a + "in", (n,)), check(a + "out", (n,)), check(a + "mix", (n, n))
+                    w[q] = f32(torch.cat([get(a + "in").float().reshape(-1), get(a + "out").float().reshape(-1),
+                                          get(a + "mix").float().reshape(-1)]))
+            if L.type == "retention":
+                rt, m = L.retention, p + "mix."
+                check(m + "q", (rt.heads * rt.dim, W)), check(m + "k", (rt.heads * rt.dim, W))
+                check(m + "v", (rt.heads * rt.vdim, W)), check(m + "g", (rt.heads * rt.vdim, W)), check(m + "o", (W, rt.heads * rt.vdim))
+                w["t_in"] = mat(m + "q", m + "k", m + "v", m + "g")
+                w["t_out"] = mat(m + "o")
+                w["t_log_decay"] = torch.log(torch.tensor(rt.decay, dtype=torch.float64)).to(torch.float32).to(device)
+                w["t_norm"] = torch.ones(rt.vdim, dtype=torch.float32, device=device)
+                if rt.rot.dims:
+                    w["rot_freq"], w["rot_mag"] = rotary(rt.rot)
+            elif L.type == "latent_attention":
+                a, m = L.latent, p + "mix."
+                check(m + "q", (a.heads * (a.dim + a.rot_dim), W)), check(m + "g", (a.heads, W))
+                check(m + "uk", (a.heads * a.dim, a.kv_rank)), check(m + "uv", (a.heads * a.vdim, a.kv_rank))
+                check(m + "o", (W, a.heads * a.vdim)), check(m + "sink", (a.heads,))
+                if a.kv_from < 0:
+                    check(m + "dkv", (a.kv_rank + a.rot_dim, W)), check(m + "dkv.norm", (a.kv_rank,))
+                    w["a_in"] = mat(m + "q", m + "dkv", m + "g")
+                    w["a_latent_norm"] = f32(get(m + "dkv.norm"))
+                else:
+                    w["a_in"] = mat(m + "q", m + "g")
+                # query absorption reads each head's key up-projection transposed: [heads][rank][dim]
+                w["a_uk_t"] = get(m + "uk").to(torch.float32).reshape(a.heads, a.dim, a.kv_rank).transpose(1, 2) \
+                    .contiguous().to(device=device, dtype=dtype)
+                w["a_uv"] = mat(m + "uv")
+                w["a_sink"] = f32(get(m + "sink"))
+                w["a_out"] = mat(m + "o")
+                w["rot_freq"], w["rot_mag"] = rotary(a.rot)
+            elif L.type == "mamba2":
                 s = L.ssd
                 m = p + "mix."
                 w["s_in"] = mat(m + "in")
@@ -117,8 +167,23 @@ class SeqWeights:
                 w["r_norm"] = f32(get(b + "norm"))
                 w["r_out"] = mat(b + "o")
                 w["r_branch_norm"] = f32(get(b + "out"))
-            if L.ff:
-                w["norm2"] = f32(get(p + "norm2"))
+            if L.moe:
+                e, m = L.moe, p + "mlp."
+                w["norm2"] = norm_w(p + "norm2")
+                for j in range(e.experts):
+                    check(f"{m}e{j}.up", (e.ff, W)), check(f"{m}e{j}.down", (W, e.ff))
+                check(m + "router", (e.experts, W)), check(m + "correction", (e.experts,))
+                w["e_up"] = torch.stack([get(f"{m}e{j}.up") for j in range(e.experts)]).to(device=device, dtype=dtype).contiguous()
+                w["e_down"] = torch.stack([get(f"{m}e{j}.down") for j in range(e.experts)]).to(device=device, dtype=dtype).contiguous()
+                w["e_correction"] = f32(get(m + "correction"))
+                if e.shared_ff:
+                    check(m + "shared.up", (e.shared_ff, W)), check(m + "shared.down", (W, e.shared_ff)), check(m + "shared.sg", (1, W))
+                    w["e_router"] = mat(m + "router", m + "shared.sg")     # the shared gate's logit is one more router row
+                    w["e_shared_up"], w["e_shared_down"] = mat(m + "shared.up"), mat(m + "shared.down")
+                else:
+                    w["e_router"] = mat(m + "router")
+            elif L.ff:
+                w["norm2"] = norm_w(p + "norm2")
                 w["ff_in"] = mat(p + "mlp.gate", p + "mlp.up")
                 w["ff_out"] = mat(p + "mlp.down")
                 if shape(p + "mlp.gate") != (L.ff, W) or shape(p + "mlp.up") != (L.ff, W):
@@ -128,7 +193,7 @@ class SeqWeights:
 
     def nbytes(self) -> int:
         n = sum(x.numel() * x.element_size() for x in (self.embed, self.head, self.final_norm))
-        return n + sum(x.numel() * x.element_size() for w in self.layers for x in w.values())
+        return n + sum(x.numel() * x.element_size() for w in self.layers for x in w.values() if isinstance(x, torch.Tensor))
 
 
 class SeqLMForCausalLM:
@@ -143,6 +208,11 @@ class SeqLMForCausalLM:
         self.ctx = _cabi.Context(device.index if device.index is not None else torch.cuda.current_device(), profile=self.PROFILE)
         self._native = self._build_native()
         attn = {i: (L.left.kv_heads, L.left.dim, L.left.vdim, L.left.chunk) for i, L in enumerate(config.layers) if L.type == "parallel"}
+        # a latent cache is one K pool of [latent | rotary key part] rows; a layer that reads another layer's cache has none
+        attn.update({i: (1, L.latent.kv_rank + L.latent.rot_dim, 0, 0) for i, L in enumerate(config.layers)
+                     if L.type == "latent_attention" and L.latent.kv_from < 0})
+        self._kv_source = {i: (L.latent.kv_from if L.latent.kv_from >= 0 else i) for i, L in enumerate(config.layers)
+                           if L.type == "latent_attention"}
         pages = (max_tokens + PAGE_SIZE - 1) // PAGE_SIZE + 2 if max_tokens else 32
         self.pool = SeqStatePool(attn, self._native.state_floats(), self.dtype, device, initial_pages=pages)
         self._ensure_workspace(max(256, min(max_tokens, 4096)) if max_tokens else 1024, 64)
@@ -177,7 +247,22 @@ class SeqLMForCausalLM:
             e = arr[i]
             e.ff = L.ff
             e.norm1_f32 = p(lw["norm1"])
-            if L.type == "mamba2":
+            e.hc1_f32, e.hc2_f32 = p(lw.get("hc1")), p(lw.get("hc2"))
+            e.a_kv_from = -1
+            e.rot_inv_freq_f32, e.rot_mag = p(lw.get("rot_freq")), lw.get("rot_mag", 1.0)
+            if L.type == "retention":
+                t = L.retention
+                e.type = _cabi.MIX_RETENTION
+                e.t_heads, e.t_dim, e.t_vdim, e.t_rot_dims = t.heads, t.dim, t.vdim, t.rot.dims
+                e.t_in, e.t_log_decay_f32, e.t_norm_f32, e.t_out = p(lw["t_in"]), p(lw["t_log_decay"]), p(lw["t_norm"]), p(lw["t_out"])
+            elif L.type == "latent_attention":
+                a = L.latent
+                e.type = _cabi.MIX_LATENT
+                e.a_heads, e.a_dim, e.a_rot_dim, e.a_vdim, e.a_rank, e.a_kv_from = a.heads, a.dim, a.rot_dim, a.vdim, a.kv_rank, a.kv_from
+                e.a_scale = a.scale
+                e.a_in, e.a_latent_norm_f32, e.a_uk_t, e.a_uv = p(lw["a_in"]), p(lw.get("a_latent_norm")), p(lw["a_uk_t"]), p(lw["a_uv"])
+                e.a_sink_f32, e.a_out = p(lw["a_sink"]), p(lw["a_out"])
+            elif L.type == "mamba2":
                 s = L.ssd
                 e.type = _cabi.MIX_SSD
                 e.s_heads, e.s_vdim, e.s_state, e.s_groups, e.s_conv, e.s_norm_groups = s.heads, s.vdim, s.state, s.groups, s.conv, s.norm_groups
@@ -194,12 +279,21 @@ class SeqLMForCausalLM:
                 e.l_out, e.l_branch_norm_f32 = p(lw["l_out"]), p(lw["l_branch_norm"])
                 e.r_in, e.r_decay_up, e.r_decay_bias_f32 = p(lw["r_in"]), p(lw["r_decay_up"]), p(lw["r_decay_bias"])
                 e.r_norm_f32, e.r_out, e.r_branch_norm_f32 = p(lw["r_norm"]), p(lw["r_out"]), p(lw["r_branch_norm"])
-            if L.ff:
+            if L.moe:
+                x = L.moe
+                e.ff_kind = _cabi.FF_MOE
+                e.e_experts, e.e_top, e.e_ff, e.e_shared_ff, e.e_scale = x.experts, x.top, x.ff, x.shared_ff, x.scale
+                e.norm2_f32, e.e_router, e.e_correction_f32 = p(lw["norm2"]), p(lw["e_router"]), p(lw["e_correction"])
+                e.e_up, e.e_down = p(lw["e_up"]), p(lw["e_down"])
+                e.e_shared_up, e.e_shared_down = p(lw.get("e_shared_up")), p(lw.get("e_shared_down"))
+            elif L.ff:
                 e.norm2_f32, e.ff_in, e.ff_out = p(lw["norm2"]), p(lw["ff_in"]), p(lw["ff_out"])
         desc = _cabi.SeqModelDesc(
             width=cfg.width, vocab=cfg.vocab, n_layers=len(cfg.layers),
             dtype=_cabi.DT_F32 if self.dtype == torch.float32 else _cabi.DT_BF16, rows_padded8=1, eps=cfg.eps, alpha=cfg.alpha,
-            embed_scale=cfg.embed_scale, logit_softcap=cfg.logit_softcap, embed=p(w.embed), inv_freq_f32=p(w.inv_freq),
+            embed_scale=cfg.embed_scale, logit_softcap=cfg.logit_softcap,
+            block=_cabi.BLOCK_PRENORM_HC if cfg.block == "prenorm_hc" else _cabi.BLOCK_POSTNORM, streams=cfg.streams,
+            embed=p(w.embed), inv_freq_f32=p(w.inv_freq),
             final_norm_f32=p(w.final_norm), head=p(w.head), layers=arr)
         return _cabi.SeqNativeModel(self.ctx, desc, keepalive=(arr, w))
 
@@ -229,8 +323,9 @@ class SeqLMForCausalLM:
         nl = len(self.config.layers)
         pool = self.pool
         st = (C.c_void_p * nl)(*[(pool.state[i][cache.slot].data_ptr() if pool.state[i] is not None else None) for i in range(nl)])
-        kp = (C.c_void_p * nl)(*[(pool.k[i].data_ptr() if i in pool.k else None) for i in range(nl)])
-        vp = (C.c_void_p * nl)(*[(pool.v[i].data_ptr() if i in pool.v else None) for i in range(nl)])
+        src = self._kv_source                       # latent-attention layers: whose K pool they read
+        kp = (C.c_void_p * nl)(*[(pool.k[src.get(i, i)].data_ptr() if src.get(i, i) in pool.k else None) for i in range(nl)])
+        vp = (C.c_void_p * nl)(*[(pool.v[i].data_ptr() if pool.v.get(i) is not None else None) for i in range(nl)])
         keep += [st, kp, vp]
         return _cabi.SeqEntry(n_new=n_new, past=cache.seq_len, ids=ids_dev.data_ptr(), page_table=cache.page_table.data_ptr(),
                               scalars=cache.scalars.data_ptr() if device_pos else None, layer_state=st, k_pages=kp, v_pages=vp)
