@@ -89,7 +89,7 @@ def latent_kv(h, w, mx, eps):
     return c, kr
 
 
-def latent_attention(h, w, mx, eps, kv):
+def latent_attention(h, w, mx, eps, kv, sink=True):
     """Causal softmax attention whose keys and values are up-projections of a shared latent; a per-head sink term in the
     denominator; a per-head sigmoid gate on the output."""
     H, D, DR, DV = int(mx["heads"]), int(mx["dim"]), int(mx["rot_dim"]), int(mx["vdim"])
@@ -106,7 +106,7 @@ def latent_attention(h, w, mx, eps, kv):
         s = s.masked_fill(torch.ones(T, T, dtype=torch.bool).triu(1), -math.inf)
         m = torch.maximum(s.max(-1).values, w["sink"][hd])
         e = torch.exp(s - m[:, None])
-        p = e / (e.sum(-1) + torch.exp(w["sink"][hd] - m))[:, None]
+        p = e / (e.sum(-1) + (torch.exp(w["sink"][hd] - m) if sink else 0.0))[:, None]
         out[:, hd] = p @ v[:, hd]
     return (out * gate[..., None]).reshape(T, H * DV) @ w["o"].T
 
@@ -115,13 +115,13 @@ def expert(h, up, down):
     return torch.relu(h @ up.T).pow(2) @ down.T
 
 
-def routed_ff(h, w, mlp):
+def routed_ff(h, w, mlp, correction=True):
     """Sigmoid router: the `top` largest of (score + correction) are chosen, their plain scores times `scale` weigh the
     experts; a shared expert runs for every token behind a scalar sigmoid gate."""
     r = mlp["router"]
     E, top, scale = int(r["experts"]), int(r["top"]), float(r["scale"])
     s = torch.sigmoid(h @ w["router"].T)
-    pick = torch.topk(s + w["correction"], top, dim=-1).indices
+    pick = torch.topk(s + (w["correction"] if correction else 0.0), top, dim=-1).indices
     out = torch.zeros(h.shape[0], w["e0.down"].shape[0], dtype=F64)
     for t in range(h.shape[0]):
         for e in pick[t].tolist():
@@ -135,8 +135,9 @@ def sub(tensors, prefix):
     return {k[len(prefix):]: v.to(F64) for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(cfg: dict, tensors: dict, tokens):
-    """Returns (logits [T, vocab], residual stream after every layer [layers, T, width]), float64."""
+def forward(cfg: dict, tensors: dict, tokens, sink=True, correction=True):
+    """Returns (logits [T, vocab], residual stream after every layer [layers, T, width]), float64. sink / correction =
+    False leave a mechanism out (tests use that to show that their weights would expose its absence)."""
     eps = float(cfg["norm"]["eps"])
     n = int(cfg.get("streams", 1))
     x0 = tensors["embed"].to(F64)[torch.tensor(list(tokens))]
@@ -151,7 +152,7 @@ def forward(cfg: dict, tensors: dict, tokens):
             u = sum(hc["in"][s] * xs[s] for s in range(n))
             h = offset_norm(u, tensors[f"{p}norm{q}"].to(F64), eps)
             if q == 2:
-                y = routed_ff(h, sub(tensors, p + "mlp."), L["mlp"])
+                y = routed_ff(h, sub(tensors, p + "mlp."), L["mlp"], correction)
             elif L["type"] == "retention":
                 y = retention(h, sub(tensors, p + "mix."), L["mixer"], eps)
             elif L["type"] == "latent_attention":
@@ -159,10 +160,18 @@ def forward(cfg: dict, tensors: dict, tokens):
                 src = L["mixer"].get("kv_from")
                 if src is None:
                     kv_of[i] = latent_kv(h, w, L["mixer"], eps)
-                y = latent_attention(h, w, L["mixer"], eps, kv_of[i if src is None else int(src)])
+                y = latent_attention(h, w, L["mixer"], eps, kv_of[i if src is None else int(src)], sink)
             else:
                 raise ValueError(L["type"])
             xs = [sum(hc["mix"][s, t] * xs[s] for s in range(n)) + hc["out"][t] * y for t in range(n)]
         dumps.append(sum(xs))
     x = offset_norm(sum(xs), tensors["final.norm"].to(F64), eps)
     return x @ tensors["head"].to(F64).T, torch.stack(dumps)
+
+
+def greedy(cfg: dict, tensors: dict, prompt, n_new):
+    """n_new greedy tokens after the prompt (the whole sequence is recomputed for every token)."""
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(forward(cfg, tensors, toks)[0][-1].argmax()))
+    return toks[len(prompt):]
