@@ -16,6 +16,7 @@ enum GemmEpilogue {
     EPI_BIAS_RESIDUAL = 5,   // C = bf16(bf16(acc + bias) + residual)     (ViT proj/fc2, mq2vl.py:479-487)
     EPI_SWIGLU = 6,          // C[:, j] = bf16(silu(bf16 gate_j) * bf16 up_j), gate/up rows interleaved by 16
     EPI_PARTIAL_F32 = 7,     // internal (split-K): fp32 partial tiles, reduced by splitk_reduce_kernel
+    EPI_RELU2 = 8,           // C = bf16(relu(acc)^2)
 };
 
 struct GemmArgs {
@@ -33,6 +34,11 @@ struct GemmArgs {
     void* splitk_ws = nullptr;
     size_t splitk_ws_bytes = 0;
     int splits = 1;
+    // Grouped problem (routed experts): B stacks `groups` matrices of N rows each; tile_group (device int32, one entry per
+    // 128-row tile of A and C) names the matrix that tile multiplies, negative = the tile holds no rows and is skipped.
+    // M is then an upper bound of the rows in use (lists are padded to whole tiles). No split-K, no CTA pairs.
+    const int* tile_group = nullptr;
+    int groups = 1;
 };
 
 int gemm_bf16_tn(const GemmArgs& a, int num_sms, cudaStream_t stream);

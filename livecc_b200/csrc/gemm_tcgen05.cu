@@ -118,6 +118,10 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], bf16* C,
                         x[2 * j + 1] += f.y;
                     }
                 }
+                if (EPI == EPI_RELU2) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) { x[j] = fmaxf(x[j], 0.f); x[j] *= x[j]; }
+                }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) x[j] = rbf(x[j]);
                 if (EPI == EPI_BIAS_QUICKGELU) {
@@ -153,7 +157,8 @@ __global__ void __launch_bounds__(384, 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, bf16* C, int M, int N,
                     int K, int ldc, const bf16* __restrict__ bias,
-                    const bf16* residual /* may alias C */, int ldr, int splits_arg /* >= 1 */, const GemmTile cfg) {
+                    const bf16* residual /* may alias C */, int ldr, int splits_arg /* >= 1 */, const GemmTile cfg,
+                    const int* __restrict__ tile_group /* null: one weight matrix */) {
     const int BLOCK_N = cfg.bn;
     const int STAGE_BYTES = A_BYTES + BLOCK_N * BLOCK_K * 2;
     // split-K exists only in the EPI_PARTIAL_F32 instantiations; everywhere else splits is the constant 1 and the
@@ -213,6 +218,9 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t phase = 0;
             for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
                 const int m_blk = tile % m_tiles, ks = (tile / m_tiles) % splits, n_blk = tile / (m_tiles * splits);
+                // grouped: the m tile's weight matrix starts at row grp * N of the stacked B; all three roles skip empty tiles
+                const int grp = tile_group ? tile_group[m_blk] : 0;
+                if (grp < 0) continue;
                 const int kb0 = ks * kbps, kb1 = min(kb0 + kbps, num_k_blocks);
                 for (int kb = kb0; kb < kb1; ++kb) {
                     mbar_wait(&empty_bar[stage], phase ^ 1);
@@ -220,7 +228,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     uint8_t* sb = sa + A_BYTES;
                     mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
                     tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BLOCK_K, m_blk * BLOCK_M);
-                    tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BLOCK_K, n_blk * BLOCK_N);
+                    tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BLOCK_K, grp * N + n_blk * BLOCK_N);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -233,6 +241,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int acc = 0;
         uint32_t acc_phase = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            if (tile_group && tile_group[tile % m_tiles] < 0) continue;
             mbar_wait(&tmem_empty[acc], acc_phase ^ 1);
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
@@ -271,6 +280,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t acc_phase = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             const int m_blk = tile % m_tiles, ks = (tile / m_tiles) % splits, n_blk = tile / (m_tiles * splits);
+            if (tile_group && tile_group[m_blk] < 0) continue;
             mbar_wait(&tmem_full[acc], acc_phase);
             tc_fence_after();
             const int row = m_blk * BLOCK_M + q * 32 + lane;
@@ -524,7 +534,7 @@ static int launch_cfg(const GemmArgs& a, int bn, int num_sms, cudaStream_t strea
     const GemmTile cfg = make_tile(bn);
     CUtensorMap ta, tb;
     if (make_tmap_bf16_2d(&ta, a.A, a.M, a.K, a.lda, BLOCK_M)) return -10;
-    if (make_tmap_bf16_2d(&tb, a.B, a.N, a.K, a.ldb, bn)) return -11;
+    if (make_tmap_bf16_2d(&tb, a.B, (int64_t)a.N * (a.tile_group ? a.groups : 1), a.K, a.ldb, bn)) return -11;
     auto kern = gemm_bf16_tn_kernel<EPI>;
     static SmemAttrOnce once;  // per template instantiation
     if (ensure_dyn_smem(once, kern, 227 * 1024)) return -12;
@@ -535,7 +545,7 @@ static int launch_cfg(const GemmArgs& a, int bn, int num_sms, cudaStream_t strea
     lcc::count_launch();
     kern<<<grid, 384, cfg.smem_bytes, stream>>>(ta, tb, (bf16*)a.C, a.M, a.N, a.K, a.ldc,
                                                 (const bf16*)a.bias, (const bf16*)a.residual,
-                                                a.ldr, splits, cfg);
+                                                a.ldr, splits, cfg, a.tile_group);
     return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }
 
@@ -580,6 +590,7 @@ static int launch_epi(const GemmArgs& a, int bn, int num_sms, cudaStream_t strea
         case EPI_RESIDUAL: return launch_cfg<EPI_RESIDUAL>(a, bn, num_sms, stream);
         case EPI_BIAS_RESIDUAL: return launch_cfg<EPI_BIAS_RESIDUAL>(a, bn, num_sms, stream);
         case EPI_SWIGLU: return launch_cfg<EPI_SWIGLU>(a, bn, num_sms, stream);
+        case EPI_RELU2: return launch_cfg<EPI_RELU2>(a, bn, num_sms, stream);
     }
     return -14;
 }
@@ -699,7 +710,9 @@ int gemm_bf16_tn(const GemmArgs& a, int num_sms, cudaStream_t stream) {
     if ((a.epi == EPI_RESIDUAL || a.epi == EPI_BIAS_RESIDUAL) && (!a.residual || (a.ldr % 8))) return -4;
     if ((a.epi == EPI_BIAS || a.epi == EPI_BIAS_QUICKGELU || a.epi == EPI_BIAS_GELU ||
          a.epi == EPI_BIAS_RESIDUAL) && !a.bias) return -5;
-    if (int r = try_splitk(a, num_sms, stream)) return r < 0 ? r : 0;
+    if (a.tile_group && a.groups < 1) return -1;
+    if (!a.tile_group)
+        if (int r = try_splitk(a, num_sms, stream)) return r < 0 ? r : 0;
     int block_n = a.block_n;
     if (block_n == 0) {
         static int forced = -1;
@@ -710,8 +723,8 @@ int gemm_bf16_tn(const GemmArgs& a, int num_sms, cudaStream_t stream) {
         block_n = forced > 0 ? forced : choose_bn(a.M, a.N, num_sms);
     }
     // block_n < 0 selects the CTA-pair kernel with tile width -block_n (explicit: tests and tuning)
-    const bool pair = block_n < 0;
-    if (pair) block_n = -block_n;
+    const bool pair = block_n < 0 && !a.tile_group && a.epi != EPI_RELU2;
+    if (block_n < 0) block_n = -block_n;
     if (block_n < 32 || block_n > 256 || (block_n % 16) || (a.epi == EPI_SWIGLU && (block_n % 32))) return -6;
     if (pair) return (block_n % 32) ? -6 : launch_epi2(a, block_n, num_sms, stream);
     return launch_epi(a, block_n, num_sms, stream);

@@ -62,21 +62,43 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     if (shared_gate && lane == 0) shared_gate[r] = sigmoid_f(z[E]);
 }
 
+// Lists padded to whole tiles of `pad` rows (pad = 1: dense lists): list e starts at the sum of the padded counts before it.
+__device__ __forceinline__ int padded(int n, int pad) { return (n + pad - 1) / pad * pad; }
+
 __global__ void moe_index_kernel(const int* __restrict__ sel, const int* __restrict__ rank, const int* __restrict__ counts, int E,
-                                 int top, int* __restrict__ row_off, int* __restrict__ pos, int* __restrict__ src_row, int S) {
+                                 int top, int pad, int* __restrict__ row_off, int* __restrict__ pos, int* __restrict__ src_row,
+                                 int* __restrict__ tile_group, int n_tiles, int S) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i <= E) {
         int o = 0;
-        for (int e = 0; e < i; ++e) o += counts[e];
+        for (int e = 0; e < i; ++e) o += padded(counts[e], pad);
         row_off[i] = o;
+    }
+    if (tile_group && i < n_tiles) {
+        // the list that owns rows [i * pad, (i + 1) * pad), or -1 past the last list
+        int o = 0, g = -1;
+        for (int e = 0; e < E; ++e) {
+            const int n = padded(counts[e], pad);
+            if (i * pad >= o && i * pad < o + n) { g = e; break; }
+            o += n;
+        }
+        tile_group[i] = g;
     }
     if (i >= S * top) return;
     const int e = sel[i];
     int o = 0;
-    for (int j = 0; j < e; ++j) o += counts[j];
+    for (int j = 0; j < e; ++j) o += padded(counts[j], pad);
     const int p = o + rank[i];
     pos[i] = p;
     src_row[p] = i / top;
+}
+
+// out[i, :] = in[src_row[i], :] for every list row (16-byte pieces); padding rows (src_row < 0) are left alone.
+__global__ void __launch_bounds__(128) moe_gather_kernel(const uint4* __restrict__ in, int ld_in16, const int* __restrict__ src_row,
+                                                         uint4* __restrict__ out, int ld_out16, int n16) {
+    const int r = src_row[blockIdx.x];
+    if (r < 0) return;
+    for (int c = threadIdx.x; c < n16; c += blockDim.x) out[(size_t)blockIdx.x * ld_out16 + c] = in[(size_t)r * ld_in16 + c];
 }
 
 template <typename T>
@@ -105,12 +127,24 @@ int moe_route(const float* logits, int ld, const float* correction, int E, int t
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 
-int moe_index(const int* sel, const int* rank, const int* counts, int E, int top, int* row_off, int* pos, int* src_row, int S,
-              cudaStream_t s) {
-    if (!sel || !rank || !counts || !row_off || !pos || !src_row || S < 1 || E < 1 || top < 1) return -2;
-    const int n = S * top > E + 1 ? S * top : E + 1;
+int moe_index(const int* sel, const int* rank, const int* counts, int E, int top, int pad, int* row_off, int* pos, int* src_row,
+              int* tile_group, int n_tiles, int S, cudaStream_t s) {
+    if (!sel || !rank || !counts || !row_off || !pos || !src_row || S < 1 || E < 1 || top < 1 || pad < 1 || (tile_group && n_tiles < 1))
+        return -2;
+    int n = S * top > E + 1 ? S * top : E + 1;
+    if (tile_group && n_tiles > n) n = n_tiles;
     count_launch();
-    moe_index_kernel<<<(n + 255) / 256, 256, 0, s>>>(sel, rank, counts, E, top, row_off, pos, src_row, S);
+    moe_index_kernel<<<(n + 255) / 256, 256, 0, s>>>(sel, rank, counts, E, top, pad, row_off, pos, src_row, tile_group, n_tiles, S);
+    return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+int moe_gather_rows(int dt, const void* in, int ld_in, const int* src_row, void* out, int ld_out, int rows, int W, cudaStream_t s) {
+    const int per16 = dt == DT_F32 ? 4 : 8;
+    if (!in || !src_row || !out || rows < 1 || W < 1 || (W % per16) || (ld_in % per16) || (ld_out % per16) ||
+        ((uintptr_t)in % 16) || ((uintptr_t)out % 16))
+        return -2;
+    count_launch();
+    moe_gather_kernel<<<rows, 128, 0, s>>>((const uint4*)in, ld_in / per16, src_row, (uint4*)out, ld_out / per16, W / per16);
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 

@@ -68,8 +68,12 @@ Dims dims_of(const lcc_seq_layer& L) {
 // write has 16-byte aligned rows.
 inline int ld8(int n) { return (n + 7) / 8 * 8; }
 
+constexpr int kMoeTile = 128;        // row tile of the grouped tensor-core GEMM: expert lists are padded to it on that route
+constexpr int kMoeTcMinRows = 256;   // routed rows (tokens x top) from which the experts run on the tensor cores
+
 struct WsLayout {
-    size_t x32, xa, proj, proj2, mid, mid2, y32, q32, f1, f2, o1, o2, xf, scan, scan_floats, xsum, moe_f, moe_i, total;
+    size_t x32, xa, proj, proj2, mid, mid2, y32, q32, f1, f2, o1, o2, xf, scan, scan_floats, xsum, moe_f, moe_i, moe_x, moe_h, moe_o, total;
+    int moe_rows;         // rows of the expert-sorted buffers: top per token, every list padded to a whole 128-row tile
     int w_proj, w_proj2, w_mid, w_y, w_q, w_f;
     int moe_e, moe_top;   // largest expert count and top-k of any layer (0: no routed feed-forward)
 };
@@ -80,7 +84,7 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     const size_t nt = NT > 0 ? NT : 1, nw = NW > 0 ? NW : 1;
     int wp = 8, wp2 = 8, wm = 8, wy = 8, wq = 8, wf = 8;
     size_t scan_floats = 0;
-    int moe_e = 0, moe_top = 0;
+    int moe_e = 0, moe_top = 0, moe_ff = 0, moe_rows = 0;
     for (const lcc_seq_layer& l : m->layers) {
         const Dims z = dims_of(l);
         if (l.type == LCC_MIX_SSD) {
@@ -101,12 +105,12 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
             wq = std::max(wq, l.a_heads * z.a_kd);
         }
         if (l.ff_kind == LCC_FF_MOE) {
-            // per row: `top` expert hidden rows in proj, `top` expert output rows in mid, the shared hidden row in mid2
-            wp = std::max(wp, l.e_top * ld8(l.e_ff)); wm = std::max(wm, std::max(l.e_top * ld8(m->d.width), ld8(l.e_shared_ff)));
-            moe_e = std::max(moe_e, l.e_experts); moe_top = std::max(moe_top, l.e_top);
+            wm = std::max(wm, ld8(l.e_shared_ff));            // the shared expert's hidden row
+            moe_e = std::max(moe_e, l.e_experts); moe_top = std::max(moe_top, l.e_top); moe_ff = std::max(moe_ff, ld8(l.e_ff));
+            moe_rows = std::max(moe_rows, (int)nt * l.e_top + (l.e_experts + 1) * kMoeTile);
         } else if (l.ff > 0) { wp = std::max(wp, ld8(2 * l.ff)); wm = std::max(wm, ld8(l.ff)); }
     }
-    L.moe_e = moe_e; L.moe_top = moe_top;
+    L.moe_e = moe_e; L.moe_top = moe_top; L.moe_rows = moe_rows;
     L.w_proj = wp; L.w_proj2 = wp2; L.w_mid = wm; L.w_y = wy; L.w_q = wq; L.w_f = wf;
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes); return o; };
@@ -116,7 +120,11 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     // routed feed-forward: fp32 [logits: E+1 | weights: top | shared gate: 1] per row; int32 [sel, rank, pos: top each |
     // src_row: top] per row, then [counts: E | row_off: E+1]
     L.moe_f = take(moe_e ? nt * (size_t)(moe_e + 2 + moe_top) * 4 : 0);
-    L.moe_i = take(moe_e ? (nt * (size_t)(4 * moe_top) + 2 * moe_e + 1) * 4 : 0);
+    L.moe_i = take(moe_e ? (nt * (size_t)(3 * moe_top) + (size_t)moe_rows + moe_rows / kMoeTile + 1 + 2 * moe_e + 1) * 4 : 0);
+    // expert-sorted rows: the gathered inputs (tensor-core route only), the hidden rows, the expert outputs
+    L.moe_x = take(moe_e && m->use_tc && m->d.dtype == LCC_DT_BF16 ? (size_t)moe_rows * ld8(W) * es : 0);
+    L.moe_h = take((size_t)moe_rows * moe_ff * es);
+    L.moe_o = take((size_t)moe_rows * (moe_e ? ld8(W) : 0) * es);
     L.xa = take(nt * ld8(W) * es);
     L.proj = take(nt * wp * es);
     L.proj2 = take(nt * wp2 * es);
@@ -145,14 +153,22 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
 // the CUDA-core kernels. bias is fp32; the tensor-core epilogue takes a copy in the storage type (bias_st; without one a
 // biased product stays on the CUDA cores). A ragged N runs on the tensor cores when the matrix rows are padded to 8.
 int linear(const lcc_seq_model* m, const void* x, int ldx, const void* W, const float* bias, void* y, int ldy,
-           bool y_f32, int M, int N, int K, cudaStream_t s, const void* bias_st = nullptr) {
+           bool y_f32, int M, int N, int K, cudaStream_t s, const void* bias_st = nullptr, int act = lcc::ACT_NONE) {
     const int Np = m->d.rows_padded8 ? ld8(N) : N;
+    if (act != lcc::ACT_NONE && bias) return -2;
     if (m->use_tc && m->d.dtype == LCC_DT_BF16 && !y_f32 && (!bias || bias_st) && M >= 16 && Np >= 32 && K >= 64 && (K % 8) == 0 &&
         (Np % 8) == 0 && ldy >= Np && (ldx % 8) == 0 && (ldy % 8) == 0) {
         lcc::GemmArgs a;
         a.A = x; a.B = W; a.C = y; a.M = M; a.N = Np; a.K = K; a.lda = ldx; a.ldb = K; a.ldc = ldy;
-        a.bias = bias ? bias_st : nullptr; a.residual = nullptr; a.ldr = 0; a.epi = bias ? lcc::EPI_BIAS : lcc::EPI_NONE; a.block_n = 0;
+        a.bias = bias ? bias_st : nullptr; a.residual = nullptr; a.ldr = 0; a.block_n = 0;
+        a.epi = act == lcc::ACT_RELU2 ? lcc::EPI_RELU2 : (bias ? lcc::EPI_BIAS : lcc::EPI_NONE);
         return lcc::gemm_bf16_tn(a, m->ctx->num_sms, s);
+    }
+    if (act != lcc::ACT_NONE) {   // the activation rides in the store of the CUDA-core kernels too
+        lcc::GroupedLinear g{};
+        g.dt = m->d.dtype; g.A = x; g.lda = ldx; g.W = W; g.ldw = K; g.C = y; g.ldc = ldy; g.c_f32 = y_f32;
+        g.groups = 1; g.M = M; g.N = N; g.K = K; g.act = act;
+        return lcc::linear_grouped(g, s);
     }
     return lcc::linear_any(m->d.dtype, x, ldx, W, K, bias, y, ldy, y_f32, M, N, K, s);
 }
@@ -482,29 +498,44 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             float* logit = mf; float* wsel = mf + (size_t)T * lde; float* sgate = wsel + (size_t)T * K;
             int* mi = (int*)(ws + L.moe_i);
             int* sel = mi; int* rank = sel + (size_t)T * K; int* posn = rank + (size_t)T * K; int* src_row = posn + (size_t)T * K;
-            int* counts = src_row + (size_t)T * K; int* row_off = counts + E;
+            int* tile_group = src_row + L.moe_rows; int* counts = tile_group + L.moe_rows / kMoeTile + 1; int* row_off = counts + E;
+            uint8_t* ex = ws + L.moe_x; uint8_t* eh = ws + L.moe_h; uint8_t* eo = ws + L.moe_o;
             const bool shared = l.e_shared_ff > 0;
+            // experts on the tensor cores: bf16, enough routed rows, 8-aligned shapes; lists are then padded to whole tiles
+            const bool tc = m->use_tc && dt == LCC_DT_BF16 && T * K >= kMoeTcMinRows && (W % 8) == 0 && (l.e_ff % 8) == 0 && W >= 64 && l.e_ff >= 64;
+            const int rows_max = T * K + E * (kMoeTile - 1), n_tiles = (rows_max + kMoeTile - 1) / kMoeTile;
             // router logits (and the shared expert's gate logit) accumulate in fp32 from the normed row
             STEP(lcc::linear_any(dt, xa, W, l.e_router, W, nullptr, logit, lde, true, T, E + (shared ? 1 : 0), W, s), "router");
             if (cudaMemsetAsync(counts, 0, sizeof(int) * E, s) != cudaSuccess) LCC_FAIL(m->ctx, -100, "router counters");
+            if (tc && cudaMemsetAsync(src_row, 0xff, sizeof(int) * (size_t)n_tiles * kMoeTile, s) != cudaSuccess) LCC_FAIL(m->ctx, -100, "row lists");
             STEP(lcc::moe_route(logit, lde, l.e_correction_f32, E, K, l.e_scale, sel, wsel, shared ? sgate : nullptr, counts, rank, T, s), "expert choice");
-            STEP(lcc::moe_index(sel, rank, counts, E, K, row_off, posn, src_row, T, s), "expert row lists");
-            lcc::GroupedLinear g{};
-            g.dt = dt; g.A = xa; g.lda = W; g.a_stride = 0; g.a_rows = src_row; g.row_off = row_off; g.M_total = T * K;
-            g.W = l.e_up; g.ldw = W; g.w_stride = (int64_t)l.e_ff * W;
-            g.C = proj; g.ldc = ldh; g.c_stride = 0; g.c_f32 = false;
-            g.groups = E; g.M = T; g.N = l.e_ff; g.K = W; g.act = lcc::ACT_RELU2;
-            STEP(lcc::linear_grouped(g, s), "experts up");
-            g.A = proj; g.lda = ldh; g.a_rows = nullptr;
-            g.W = l.e_down; g.ldw = l.e_ff; g.w_stride = (int64_t)W * l.e_ff;
-            g.C = mid; g.ldc = ldw8; g.N = W; g.K = l.e_ff; g.act = lcc::ACT_NONE;
-            STEP(lcc::linear_grouped(g, s), "experts down");
+            STEP(lcc::moe_index(sel, rank, counts, E, K, tc ? kMoeTile : 1, row_off, posn, src_row, tc ? tile_group : nullptr, n_tiles, T, s), "expert row lists");
+            if (tc) {
+                STEP(lcc::moe_gather_rows(dt, xa, W, src_row, ex, ldw8, n_tiles * kMoeTile, W, s), "expert row gather");
+                lcc::GemmArgs a;
+                a.A = ex; a.B = l.e_up; a.C = eh; a.M = n_tiles * kMoeTile; a.N = l.e_ff; a.K = W; a.lda = ldw8; a.ldb = W; a.ldc = ldh;
+                a.bias = nullptr; a.residual = nullptr; a.ldr = 0; a.epi = lcc::EPI_RELU2; a.block_n = 0;
+                a.tile_group = tile_group; a.groups = E;
+                STEP(lcc::gemm_bf16_tn(a, m->ctx->num_sms, s), "experts up");
+                a.A = eh; a.B = l.e_down; a.C = eo; a.N = W; a.K = l.e_ff; a.lda = ldh; a.ldb = l.e_ff; a.ldc = ldw8; a.epi = lcc::EPI_NONE;
+                STEP(lcc::gemm_bf16_tn(a, m->ctx->num_sms, s), "experts down");
+            } else {
+                lcc::GroupedLinear g{};
+                g.dt = dt; g.A = xa; g.lda = W; g.a_stride = 0; g.a_rows = src_row; g.row_off = row_off; g.M_total = T * K;
+                g.W = l.e_up; g.ldw = W; g.w_stride = (int64_t)l.e_ff * W;
+                g.C = eh; g.ldc = ldh; g.c_stride = 0; g.c_f32 = false;
+                g.groups = E; g.M = T; g.N = l.e_ff; g.K = W; g.act = lcc::ACT_RELU2;
+                STEP(lcc::linear_grouped(g, s), "experts up");
+                g.A = eh; g.lda = ldh; g.a_rows = nullptr;
+                g.W = l.e_down; g.ldw = l.e_ff; g.w_stride = (int64_t)W * l.e_ff;
+                g.C = eo; g.ldc = ldw8; g.N = W; g.K = l.e_ff; g.act = lcc::ACT_NONE;
+                STEP(lcc::linear_grouped(g, s), "experts down");
+            }
             if (shared) {
-                STEP(linear(m, xa, W, l.e_shared_up, nullptr, mid2, lds, false, T, l.e_shared_ff, W, s), "shared expert up");
-                STEP(lcc::relu_squared(dt, mid2, lds, mid2, lds, T, l.e_shared_ff, s), "shared expert activation");
+                STEP(linear(m, xa, W, l.e_shared_up, nullptr, mid2, lds, false, T, l.e_shared_ff, W, s, nullptr, lcc::ACT_RELU2), "shared expert up");
                 STEP(linear(m, mid2, lds, l.e_shared_down, nullptr, o2, W, false, T, W, l.e_shared_ff, s), "shared expert down");
             }
-            STEP(lcc::moe_combine(dt, mid, ldw8, posn, wsel, K, shared ? o2 : nullptr, W, sgate, o1, W, T, W, s), "expert combine");
+            STEP(lcc::moe_combine(dt, eo, ldw8, posn, wsel, K, shared ? o2 : nullptr, W, sgate, o1, W, T, W, s), "expert combine");
         } else if (l.ff > 0) {
             const int ldg = ld8(2 * l.ff), ldf = ld8(l.ff);
             STEP(linear(m, xa, W, l.ff_in, nullptr, proj, ldg, false, T, 2 * l.ff, W, s), "feed-forward in");

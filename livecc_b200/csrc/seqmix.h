@@ -162,10 +162,14 @@ int hyper_boundary(int dt, float* xs, int n, const void* y, int ld_y, const floa
 // receives the number of rows per expert; rank int32 [S, top] = the row's arrival number inside its expert.
 int moe_route(const float* logits, int ld, const float* correction, int E, int top, float scale, int* sel, float* weight,
               float* shared_gate, int* counts, int* rank, int S, cudaStream_t s);
-// row_off int32 [E+1] = exclusive prefix sum of counts; pos[r, k] = row_off[sel] + rank = the row's place in the expert-sorted
-// list; src_row[pos] = r.
-int moe_index(const int* sel, const int* rank, const int* counts, int E, int top, int* row_off, int* pos, int* src_row, int S,
-              cudaStream_t s);
+// Expert-sorted row lists. Each list is padded to a multiple of `pad` rows (1: dense). row_off int32 [E+1] = start of every
+// list (row_off[E] = total); pos[r, k] = row_off[sel] + rank = the row's place; src_row[pos] = r (entries of padding rows
+// are not written: fill src_row with -1 first when pad > 1). tile_group (optional, int32 [n_tiles]): the list that owns
+// rows [i * pad, (i + 1) * pad), -1 past the end: the tile table of a grouped tensor-core GEMM.
+int moe_index(const int* sel, const int* rank, const int* counts, int E, int top, int pad, int* row_off, int* pos, int* src_row,
+              int* tile_group, int n_tiles, int S, cudaStream_t s);
+// out[i, :] = in[src_row[i], :] for rows with src_row[i] >= 0 (storage dt; W, leading dimensions and bases 16-byte aligned)
+int moe_gather_rows(int dt, const void* in, int ld_in, const int* src_row, void* out, int ld_out, int rows, int W, cudaStream_t s);
 // out[r, :] = sum_k weight[r, k] * eo[pos[r, k], :] (+ shared_gate[r] * so[r, :])   (eo, so, out: storage dt)
 int moe_combine(int dt, const void* eo, int ld_eo, const int* pos, const float* weight, int top, const void* so, int ld_so,
                 const float* shared_gate, void* out, int ld_out, int S, int W, cudaStream_t s);

@@ -240,6 +240,28 @@ def test_many_rows_per_expert_and_experts_without_rows():
     assert rel(run(m, toks, [280, 290] + list(range(291, 300))), want) < F32_TOL
 
 
+def test_experts_on_the_tensor_cores(monkeypatch):
+    """bf16 storage with enough routed rows and 8-aligned expert shapes: expert lists are padded to whole 128-row tiles and
+    both expert products run as one grouped tensor-core GEMM each (relu^2 in the first one's epilogue). 400 tokens over 5
+    experts (lists longer than a tile, ragged last tiles) and over 9 experts with top 1 (some lists shorter than a tile);
+    against the oracle, against the CUDA-core route, and with the prompt cut so that later portions take the few-row route."""
+    layers = [K.lat(heads=2, dim=8, rot_dim=8, vdim=8, kv_rank=16, mlp=K.moe(experts=5, top=2, ff=72, scale=1.0, shared=80)),
+              K.ret(heads=2, dim=8, vdim=8, decay=(0.9, 0.95), rot_dims=4, mlp=K.moe(experts=9, top=1, ff=64, scale=2.0, shared=0))]
+    d = K.config(layers, width=64, vocab=64)
+    tensors = synthetic_seq_tensors(SeqModelConfig.from_json(d), seed=25)
+    toks = K.tokens(400, d["vocab"], seed=54)
+    want = O.forward(d, tensors, toks)[0]
+    m = build(d, tensors, "bfloat16")
+    n0 = m.kernel_launches()
+    got = run(m, toks, [])
+    assert m.kernel_launches() - n0 < 60, "the step took the per-list kernels"
+    assert bf16_ok(got, want)
+    assert bf16_ok(run(m, toks, [300, 390, 395]), want)
+    monkeypatch.setenv("LIVECC_B200_SEQ_TC", "0")
+    assert bf16_ok(run(build(d, tensors, "bfloat16"), toks, []), want)
+    assert rel(run(build(d, tensors, "float32"), toks, []), want) < F32_TOL
+
+
 # ---- batches, pages and slots that are used again -----------------------------------------------------------------------------
 def test_a_batch_of_unequal_requests_equals_each_alone():
     m, d, _ = model_of("mixed")
