@@ -39,6 +39,13 @@ struct GemmArgs {
     // M is then an upper bound of the rows in use (lists are padded to whole tiles). No split-K, no CTA pairs.
     const int* tile_group = nullptr;
     int groups = 1;
+    // Batched problem (per-head projections): `batch` products in one launch; product z reads columns z * a_col_stride .. of
+    // A, the z-th matrix of N rows of the stacked B, and writes columns z * c_col_stride .. of C (strides in elements,
+    // multiples of 8). No split-K, no CTA pairs.
+    int batch = 1;
+    int a_col_stride = 0, c_col_stride = 0;
+    // fp32 output: C is float [M, ldc] (ldc a multiple of 4), epi must be EPI_NONE
+    bool c_f32 = false;
 };
 
 int gemm_bf16_tn(const GemmArgs& a, int num_sms, cudaStream_t stream);

@@ -158,7 +158,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, bf16* C, int M, int N,
                     int K, int ldc, const bf16* __restrict__ bias,
                     const bf16* residual /* may alias C */, int ldr, int splits_arg /* >= 1 */, const GemmTile cfg,
-                    const int* __restrict__ tile_group /* null: one weight matrix */) {
+                    const int* __restrict__ tile_group /* null: one weight matrix */, int batch, int a_col_stride, int c_col_stride) {
     const int BLOCK_N = cfg.bn;
     const int STAGE_BYTES = A_BYTES + BLOCK_N * BLOCK_K * 2;
     // split-K exists only in the EPI_PARTIAL_F32 instantiations; everywhere else splits is the constant 1 and the
@@ -184,7 +184,9 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // Work unit = (m tile, k split, n tile), m fastest so that the CTAs that share a weight tile run together.
     // splits == 1: a unit is a whole output tile. splits > 1 (EPI_PARTIAL_F32): a unit covers kbps k-blocks and
     // writes an fp32 partial tile; splitk_reduce_kernel sums the partials and applies the epilogue.
-    const int num_tiles = m_tiles * n_tiles * splits;
+    // batched: the products of all batch entries are one list of tiles; entry z = tile / per_z (splits == 1 there)
+    const int per_z = m_tiles * n_tiles * splits;
+    const int num_tiles = per_z * batch;
     const int kbps = (num_k_blocks + splits - 1) / splits;
 
     if (warp == 0 && lane == 0) {
@@ -216,10 +218,11 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
-            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            for (int tile_all = blockIdx.x; tile_all < num_tiles; tile_all += gridDim.x) {
+                const int z = tile_all / per_z, tile = tile_all - z * per_z;
                 const int m_blk = tile % m_tiles, ks = (tile / m_tiles) % splits, n_blk = tile / (m_tiles * splits);
                 // grouped: the m tile's weight matrix starts at row grp * N of the stacked B; all three roles skip empty tiles
-                const int grp = tile_group ? tile_group[m_blk] : 0;
+                const int grp = tile_group ? tile_group[m_blk] : z;
                 if (grp < 0) continue;
                 const int kb0 = ks * kbps, kb1 = min(kb0 + kbps, num_k_blocks);
                 for (int kb = kb0; kb < kb1; ++kb) {
@@ -227,7 +230,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     uint8_t* sa = smem + stage * STAGE_BYTES;
                     uint8_t* sb = sa + A_BYTES;
                     mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
-                    tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BLOCK_K, m_blk * BLOCK_M);
+                    tma_load_2d(sa, &tmap_a, &full_bar[stage], z * a_col_stride + kb * BLOCK_K, m_blk * BLOCK_M);
                     tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BLOCK_K, grp * N + n_blk * BLOCK_N);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -240,7 +243,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t phase = 0;
         int acc = 0;
         uint32_t acc_phase = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        for (int tile_all = blockIdx.x; tile_all < num_tiles; tile_all += gridDim.x) {
+            const int tile = tile_all % per_z;
             if (tile_group && tile_group[tile % m_tiles] < 0) continue;
             mbar_wait(&tmem_empty[acc], acc_phase ^ 1);
             tc_fence_after();
@@ -278,7 +282,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int c_begin = half ? chunks_h0 : 0, c_end = half ? chunks : chunks_h0;
         int acc = 0;
         uint32_t acc_phase = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        for (int tile_all = blockIdx.x; tile_all < num_tiles; tile_all += gridDim.x) {
+            const int z = tile_all / per_z, tile = tile_all - z * per_z;
             const int m_blk = tile % m_tiles, ks = (tile / m_tiles) % splits, n_blk = tile / (m_tiles * splits);
             if (tile_group && tile_group[m_blk] < 0) continue;
             mbar_wait(&tmem_full[acc], acc_phase);
@@ -294,7 +299,10 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 tmem_ld_32x32b_x32(taddr, v);
                 tmem_ld_wait();
                 const int col0 = n_blk * BLOCK_N + c * 32;
-                epilogue_chunk<EPI>(v, C, ldc, M, row, row_ok, col0, tile_end, ks, bias, residual, ldr);
+                // batched: entry z's columns start at z * c_col_stride (floats when the output is fp32)
+                bf16* Cz = (EPI == EPI_PARTIAL_F32) ? reinterpret_cast<bf16*>(reinterpret_cast<float*>(C) + (size_t)z * c_col_stride)
+                                                    : C + (size_t)z * c_col_stride;
+                epilogue_chunk<EPI>(v, Cz, ldc, M, row, row_ok, col0, tile_end, ks, bias, residual, ldr);
             }
             tc_fence_before();
             __syncwarp();
@@ -533,19 +541,21 @@ template <int EPI>
 static int launch_cfg(const GemmArgs& a, int bn, int num_sms, cudaStream_t stream) {
     const GemmTile cfg = make_tile(bn);
     CUtensorMap ta, tb;
-    if (make_tmap_bf16_2d(&ta, a.A, a.M, a.K, a.lda, BLOCK_M)) return -10;
-    if (make_tmap_bf16_2d(&tb, a.B, (int64_t)a.N * (a.tile_group ? a.groups : 1), a.K, a.ldb, bn)) return -11;
+    const int batch = a.batch > 1 ? a.batch : 1;
+    // batched: A's map spans every entry's columns (a k-block that runs past an entry's K meets zero columns of B)
+    if (make_tmap_bf16_2d(&ta, a.A, a.M, batch > 1 ? (int64_t)(batch - 1) * a.a_col_stride + a.K : a.K, a.lda, BLOCK_M)) return -10;
+    if (make_tmap_bf16_2d(&tb, a.B, (int64_t)a.N * (a.tile_group ? a.groups : batch), a.K, a.ldb, bn)) return -11;
     auto kern = gemm_bf16_tn_kernel<EPI>;
     static SmemAttrOnce once;  // per template instantiation
     if (ensure_dyn_smem(once, kern, 227 * 1024)) return -12;
     const int m_tiles = (a.M + BLOCK_M - 1) / BLOCK_M, n_tiles = (a.N + bn - 1) / bn;
     const int splits = (EPI == EPI_PARTIAL_F32 && a.splits > 1) ? a.splits : 1;
-    const int tiles = m_tiles * n_tiles * splits;
+    const int tiles = m_tiles * n_tiles * splits * batch;
     const int grid = tiles < num_sms ? tiles : num_sms;
     lcc::count_launch();
     kern<<<grid, 384, cfg.smem_bytes, stream>>>(ta, tb, (bf16*)a.C, a.M, a.N, a.K, a.ldc,
                                                 (const bf16*)a.bias, (const bf16*)a.residual,
-                                                a.ldr, splits, cfg, a.tile_group);
+                                                a.ldr, splits, cfg, a.tile_group, batch, a.a_col_stride, a.c_col_stride);
     return cudaGetLastError() == cudaSuccess ? 0 : -13;
 }
 
@@ -705,13 +715,16 @@ static int try_splitk(const GemmArgs& a, int num_sms, cudaStream_t stream) {
 
 int gemm_bf16_tn(const GemmArgs& a, int num_sms, cudaStream_t stream) {
     if (a.M <= 0 || a.N <= 0 || a.K <= 0) return -1;
-    if ((a.K % 8) || (a.lda % 8) || (a.ldb % 8) || (a.N % 8) || (a.ldc % 8)) return -2;
+    if ((a.K % 8) || (a.lda % 8) || (a.ldb % 8) || (a.N % 8) || (a.ldc % (a.c_f32 ? 4 : 8))) return -2;
     if (a.epi == EPI_SWIGLU && (a.N % 32)) return -3;
     if ((a.epi == EPI_RESIDUAL || a.epi == EPI_BIAS_RESIDUAL) && (!a.residual || (a.ldr % 8))) return -4;
     if ((a.epi == EPI_BIAS || a.epi == EPI_BIAS_QUICKGELU || a.epi == EPI_BIAS_GELU ||
          a.epi == EPI_BIAS_RESIDUAL) && !a.bias) return -5;
     if (a.tile_group && a.groups < 1) return -1;
-    if (!a.tile_group)
+    const bool plain = !a.tile_group && a.batch <= 1 && !a.c_f32;
+    if (a.batch > 1 && (a.tile_group || (a.K % BLOCK_K) || (a.a_col_stride % 8) || (a.c_col_stride % 8) || a.a_col_stride < 0 || a.c_col_stride < 0)) return -7;
+    if (a.c_f32 && (a.epi != EPI_NONE || (a.ldc % 4))) return -8;
+    if (plain)
         if (int r = try_splitk(a, num_sms, stream)) return r < 0 ? r : 0;
     int block_n = a.block_n;
     if (block_n == 0) {
@@ -723,10 +736,15 @@ int gemm_bf16_tn(const GemmArgs& a, int num_sms, cudaStream_t stream) {
         block_n = forced > 0 ? forced : choose_bn(a.M, a.N, num_sms);
     }
     // block_n < 0 selects the CTA-pair kernel with tile width -block_n (explicit: tests and tuning)
-    const bool pair = block_n < 0 && !a.tile_group && a.epi != EPI_RELU2;
+    const bool pair = block_n < 0 && plain && a.epi != EPI_RELU2;
     if (block_n < 0) block_n = -block_n;
     if (block_n < 32 || block_n > 256 || (block_n % 16) || (a.epi == EPI_SWIGLU && (block_n % 32))) return -6;
     if (pair) return (block_n % 32) ? -6 : launch_epi2(a, block_n, num_sms, stream);
+    if (a.c_f32) {   // the fp32 tile store of the split-K instantiation, as one split
+        GemmArgs p = a;
+        p.splits = 1;
+        return launch_cfg<EPI_PARTIAL_F32>(p, block_n, num_sms, stream);
+    }
     return launch_epi(a, block_n, num_sms, stream);
 }
 

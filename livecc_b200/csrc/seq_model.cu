@@ -119,7 +119,7 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     L.xsum = take(m->d.block == LCC_BLOCK_PRENORM_HC ? nt * W * 4 : 0);
     // routed feed-forward: fp32 [logits: E+1 | weights: top | shared gate: 1] per row; int32 [sel, rank, pos: top each |
     // src_row: top] per row, then [counts: E | row_off: E+1]
-    L.moe_f = take(moe_e ? nt * (size_t)(moe_e + 2 + moe_top) * 4 : 0);
+    L.moe_f = take(moe_e ? nt * (size_t)(ld8(moe_e + 1) + 1 + moe_top) * 4 : 0);
     L.moe_i = take(moe_e ? (nt * (size_t)(3 * moe_top) + (size_t)moe_rows + moe_rows / kMoeTile + 1 + 2 * moe_e + 1) * 4 : 0);
     // expert-sorted rows: the gathered inputs (tensor-core route only), the hidden rows, the expert outputs
     L.moe_x = take(moe_e && m->use_tc && m->d.dtype == LCC_DT_BF16 ? (size_t)moe_rows * ld8(W) * es : 0);
@@ -156,9 +156,10 @@ int linear(const lcc_seq_model* m, const void* x, int ldx, const void* W, const 
            bool y_f32, int M, int N, int K, cudaStream_t s, const void* bias_st = nullptr, int act = lcc::ACT_NONE) {
     const int Np = m->d.rows_padded8 ? ld8(N) : N;
     if (act != lcc::ACT_NONE && bias) return -2;
-    if (m->use_tc && m->d.dtype == LCC_DT_BF16 && !y_f32 && (!bias || bias_st) && M >= 16 && Np >= 32 && K >= 64 && (K % 8) == 0 &&
-        (Np % 8) == 0 && ldy >= Np && (ldx % 8) == 0 && (ldy % 8) == 0) {
+    if (m->use_tc && m->d.dtype == LCC_DT_BF16 && (!y_f32 || (!bias && act == lcc::ACT_NONE)) && (!bias || bias_st) && M >= 16 &&
+        (Np >= 32 || y_f32) && K >= 64 && (K % 8) == 0 && (Np % 8) == 0 && ldy >= Np && (ldx % 8) == 0 && (ldy % 8) == 0) {
         lcc::GemmArgs a;
+        a.c_f32 = y_f32;
         a.A = x; a.B = W; a.C = y; a.M = M; a.N = Np; a.K = K; a.lda = ldx; a.ldb = K; a.ldc = ldy;
         a.bias = bias ? bias_st : nullptr; a.residual = nullptr; a.ldr = 0; a.block_n = 0;
         a.epi = act == lcc::ACT_RELU2 ? lcc::EPI_RELU2 : (bias ? lcc::EPI_BIAS : lcc::EPI_NONE);
@@ -171,6 +172,26 @@ int linear(const lcc_seq_model* m, const void* x, int ldx, const void* W, const 
         return lcc::linear_grouped(g, s);
     }
     return lcc::linear_any(m->d.dtype, x, ldx, W, K, bias, y, ldy, y_f32, M, N, K, s);
+}
+
+// Per-head products: head h multiplies columns h * a_stride .. of x with the h-th [N, K] matrix of W and writes columns
+// h * c_stride .. of y. One batched tensor-core GEMM when the shapes allow it, else the grouped CUDA-core kernels.
+int linear_heads(const lcc_seq_model* m, const void* x, int ldx, int a_stride, const void* W, void* y, int ldy, int c_stride,
+                 bool y_f32, int heads, int M, int N, int K, cudaStream_t s) {
+    if (m->use_tc && m->d.dtype == LCC_DT_BF16 && M >= 16 && N >= 32 && (K % 64) == 0 && (N % 8) == 0 && (ldx % 8) == 0 &&
+        (ldy % 8) == 0 && (a_stride % 8) == 0 && (c_stride % 8) == 0) {
+        lcc::GemmArgs a;
+        a.A = x; a.B = W; a.C = y; a.M = M; a.N = N; a.K = K; a.lda = ldx; a.ldb = K; a.ldc = ldy;
+        a.bias = nullptr; a.residual = nullptr; a.ldr = 0; a.epi = lcc::EPI_NONE; a.block_n = 0;
+        a.batch = heads; a.a_col_stride = a_stride; a.c_col_stride = c_stride; a.c_f32 = y_f32;
+        return lcc::gemm_bf16_tn(a, m->ctx->num_sms, s);
+    }
+    lcc::GroupedLinear g{};
+    g.dt = m->d.dtype; g.A = x; g.lda = ldx; g.a_stride = a_stride;
+    g.W = W; g.ldw = K; g.w_stride = (int64_t)N * K;
+    g.C = y; g.ldc = ldy; g.c_stride = c_stride; g.c_f32 = y_f32;
+    g.groups = heads; g.M = M; g.N = N; g.K = K;
+    return lcc::linear_grouped(g, s);
 }
 
 }  // namespace
@@ -375,14 +396,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                                            page_size, en.n_new, H, l.a_dim, l.a_rot_dim, l.a_rank, pos_of(en), s), "latent cache append");
                 r0 += en.n_new;
             }
-            {
-                lcc::GroupedLinear g{};
-                g.dt = dt; g.A = proj; g.lda = ldp; g.a_stride = QH;
-                g.W = l.a_uk_t; g.ldw = l.a_dim; g.w_stride = (int64_t)l.a_rank * l.a_dim;
-                g.C = q32; g.ldc = H * z.a_kd; g.c_stride = z.a_kd; g.c_f32 = true;
-                g.groups = H; g.M = T; g.N = l.a_rank; g.K = l.a_dim;
-                STEP(lcc::linear_grouped(g, s), "query absorption");
-            }
+            STEP(linear_heads(m, proj, ldp, QH, l.a_uk_t, q32, H * z.a_kd, z.a_kd, true, H, T, l.a_rank, l.a_dim, s), "query absorption");
             r0 = 0;
             for (int e = 0; e < n_entries; ++e) {
                 const lcc_seq_entry& en = entries[e];
@@ -391,14 +405,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                                           z.a_kd, l.a_rank, 0, l.a_scale, m->use_tc, pos_of(en), s, l.a_sink_f32, z.a_kd), "latent attention");
                 r0 += en.n_new;
             }
-            {
-                lcc::GroupedLinear g{};
-                g.dt = dt; g.A = mid; g.lda = ldl; g.a_stride = l.a_rank;
-                g.W = l.a_uv; g.ldw = l.a_rank; g.w_stride = (int64_t)l.a_vdim * l.a_rank;
-                g.C = mid2; g.ldc = ldo; g.c_stride = l.a_vdim; g.c_f32 = false;
-                g.groups = H; g.M = T; g.N = l.a_vdim; g.K = l.a_rank;
-                STEP(lcc::linear_grouped(g, s), "value up-projection");
-            }
+            STEP(linear_heads(m, mid, ldl, l.a_rank, l.a_uv, mid2, ldo, l.a_vdim, false, H, T, l.a_vdim, l.a_rank, s), "value up-projection");
             STEP(linear(m, mid2, ldo, l.a_out, nullptr, o1, W, false, T, W, z.a_o, s), "latent attention out-proj");
         } else if (l.type == LCC_MIX_SSD) {
             const int ldp = ld8(z.s_proj), ldm = ld8(z.conv_ch), GN = l.s_groups * l.s_state;
@@ -493,7 +500,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
         const bool has_ff = l.ff > 0 || l.ff_kind == LCC_FF_MOE;
         if (has_ff && hc) STEP(boundary(l.hc2_f32, l.norm2_f32, nullptr), "stream boundary");
         if (l.ff_kind == LCC_FF_MOE) {
-            const int E = l.e_experts, K = l.e_top, lde = E + 1, ldh = ld8(l.e_ff), ldw8 = ld8(W), lds = ld8(l.e_shared_ff);
+            const int E = l.e_experts, K = l.e_top, lde = ld8(E + 1), ldh = ld8(l.e_ff), ldw8 = ld8(W), lds = ld8(l.e_shared_ff);
             float* mf = (float*)(ws + L.moe_f);
             float* logit = mf; float* wsel = mf + (size_t)T * lde; float* sgate = wsel + (size_t)T * K;
             int* mi = (int*)(ws + L.moe_i);
@@ -505,7 +512,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             const bool tc = m->use_tc && dt == LCC_DT_BF16 && T * K >= kMoeTcMinRows && (W % 8) == 0 && (l.e_ff % 8) == 0 && W >= 64 && l.e_ff >= 64;
             const int rows_max = T * K + E * (kMoeTile - 1), n_tiles = (rows_max + kMoeTile - 1) / kMoeTile;
             // router logits (and the shared expert's gate logit) accumulate in fp32 from the normed row
-            STEP(lcc::linear_any(dt, xa, W, l.e_router, W, nullptr, logit, lde, true, T, E + (shared ? 1 : 0), W, s), "router");
+            STEP(linear(m, xa, W, l.e_router, nullptr, logit, lde, true, T, E + (shared ? 1 : 0), W, s), "router");
             if (cudaMemsetAsync(counts, 0, sizeof(int) * E, s) != cudaSuccess) LCC_FAIL(m->ctx, -100, "router counters");
             if (tc && cudaMemsetAsync(src_row, 0xff, sizeof(int) * (size_t)n_tiles * kMoeTile, s) != cudaSuccess) LCC_FAIL(m->ctx, -100, "row lists");
             STEP(lcc::moe_route(logit, lde, l.e_correction_f32, E, K, l.e_scale, sel, wsel, shared ? sgate : nullptr, counts, rank, T, s), "expert choice");

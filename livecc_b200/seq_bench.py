@@ -40,6 +40,32 @@ def seq_config(width: int, n_layers: int, ff: int, chunk: int, vocab: int = 3276
                                      "logit_softcap": 50.0})
 
 
+def kedelorn_config(width: int, n_layers: int, ff: int, vocab: int = 32768) -> SeqModelConfig:
+    """Two residual streams; layers in the pattern latent attention, latent attention reading the first one's cache,
+    retention, retention. Latent attention: 128 + 64 channel query heads, 192 latent + 64 rotary cache channels per token,
+    128-channel values. Retention: 128-channel keys, 256-channel values, decays 1 - 2^-(5+h). Every layer has 16 experts
+    of width ff/4 (2 per token) and a shared expert of width ff/2: the active feed-forward width per token equals the dense
+    `ff` of the models beside it."""
+    heads, layers = width // 128, []
+    rot = {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    mlp = {"kind": "moe", "expert": {"ff": ff // 4 // 8 * 8}, "router": {"experts": 16, "top": 2, "scale": 2.5},
+           "shared": {"ff": ff // 2 // 8 * 8}}
+    for i in range(n_layers):
+        k = i % 4
+        if k < 2:
+            mx = dict(heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=192, scale=192 ** -0.5, rot=rot)
+            if k == 1:
+                mx["kv_from"] = i - 1
+            layers.append({"type": "latent_attention", "mixer": mx, "mlp": mlp})
+        else:
+            rh = width // 256
+            layers.append({"type": "retention", "mlp": mlp,
+                           "mixer": dict(heads=rh, dim=128, vdim=256, decay=[1.0 - 2.0 ** (-5 - (h % 8)) for h in range(rh)],
+                                         rot={"dims": 128, "base": 10000.0})})
+    return SeqModelConfig.from_json({"architecture": "Kedelorn", "vocab": vocab, "width": width, "streams": 2, "layers": layers,
+                                     "norm": {"eps": 1e-6}})
+
+
 def qwen_config(width: int, n_layers: int, ff: int, vocab: int = 32768) -> LiveCCConfig:
     heads = width // 128
     return LiveCCConfig(
@@ -87,21 +113,38 @@ def time_qwen(model, prompt_len: int, new_tokens: int, steps: int, warmup: int) 
             "decode_tok_s": 1e3 / _median(dec)}
 
 
-def run(sizes: List[str], prompt_lens: List[int], new_tokens: int, steps: int, warmup: int, dtype: str = "bfloat16") -> Dict:
+def active_weight_bytes(model) -> int:
+    """Bytes of weights one decode step reads: everything but the embedding table (one row is read) and, in a routed
+    feed-forward, the experts that were not chosen."""
+    n = model.weights.nbytes() - model.weights.embed.numel() * model.weights.embed.element_size()
+    for L, w in zip(model.config.layers, model.weights.layers):
+        if L.moe:
+            per = (w["e_up"].numel() + w["e_down"].numel()) * w["e_up"].element_size() // L.moe.experts
+            n -= per * (L.moe.experts - L.moe.top)
+    return n
+
+
+def run(sizes: List[str], prompt_lens: List[int], new_tokens: int, steps: int, warmup: int, dtype: str = "bfloat16",
+        design: str = "Bimopel") -> Dict:
     from .engine import LiveCCB200ForConditionalGeneration
     from .seq_engine import SeqLMForCausalLM
 
     out = {}
     for name in sizes:
         width, n_layers, ff, chunk = SIZES[name]
-        cfg = seq_config(width, n_layers, ff, chunk)
-        m = SeqLMForCausalLM.from_state_dict(cfg, synthetic_seq_tensors(cfg, seed=7, device="cuda"), dtype,
-                                             max_tokens=max(prompt_lens) + new_tokens + 64)
-        rec = {"weights_gb": round(m.weights.nbytes() / 1e9, 3), "bimopel": {}, "qwen2": {}}
-        for S in prompt_lens:
-            rec["bimopel"][f"S{S}"] = time_seq(m, S, new_tokens, steps, warmup)
-        del m
-        torch.cuda.empty_cache()
+        rec = {}
+        for label, cfg in ([("kedelorn", kedelorn_config(width, n_layers, ff))] if design == "Kedelorn" else []) + \
+                [("bimopel", seq_config(width, n_layers, ff, chunk))]:
+            m = SeqLMForCausalLM.from_state_dict(cfg, synthetic_seq_tensors(cfg, seed=7, device="cuda"), dtype,
+                                                 max_tokens=max(prompt_lens) + new_tokens + 64)
+            rec["weights_gb" if label == "bimopel" else label + "_weights_gb"] = round(m.weights.nbytes() / 1e9, 3)
+            rec[label + "_decode_read_gb"] = round(active_weight_bytes(m) / 1e9, 3)
+            rec[label] = {}
+            for S in prompt_lens:
+                rec[label][f"S{S}"] = time_seq(m, S, new_tokens, steps, warmup)
+            del m
+            torch.cuda.empty_cache()
+        rec["qwen2"] = {}
         q = LiveCCB200ForConditionalGeneration.from_synthetic(qwen_config(width, n_layers, ff))
         rec["qwen2_weights_gb"] = round(q.weights.nbytes() / 1e9, 3)
         for S in prompt_lens:
@@ -112,15 +155,16 @@ def run(sizes: List[str], prompt_lens: List[int], new_tokens: int, steps: int, w
     return out
 
 
-def main(args) -> Dict:
-    """bench.py --arch seq: one JSON line; `value` = decode tokens/s of the first size at the first prompt length."""
+def main(args, design: str = "Bimopel") -> Dict:
+    """bench.py --arch seq | kedelorn: one JSON line; `value` = decode tokens/s of the first size at the first prompt length."""
     sizes = [s for s in (args.seq_sizes.split(",") if args.seq_sizes else list(SIZES)) if s in SIZES]
     lens = [int(x) for x in args.seq_prompt.split(",")]
-    res = run(sizes, lens, args.max_new_tokens if args.max_new_tokens > 16 else 64, args.steps, max(args.warmup, 3))
-    first = res[sizes[0]]["bimopel"][f"S{lens[0]}"]
+    res = run(sizes, lens, args.max_new_tokens if args.max_new_tokens > 16 else 64, args.steps, max(args.warmup, 3), design=design)
+    first = res[sizes[0]][design.lower()][f"S{lens[0]}"]
     return {"metric": "decode_tokens_per_s", "value": first["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": first["decode_ms_per_token"], "higher_is_better": True, "dtype": "bf16",
             "data": "synthetic (random weights, random ids)", "vs_baseline": None,
-            "config": {"model": f"Bimopel {sizes[0]} beside Qwen2-style decoder of equal width/depth/ff", "global_batch": 1,
+            "config": {"model": f"{design} {sizes[0]} beside " + ("Bimopel and the " if design == "Kedelorn" else "") +
+                                "Qwen2-style decoder of equal width/depth/ff", "global_batch": 1,
                        "seq_len": lens[0], "parallelism": "1 gpu", "l2": "weights of every size exceed L2"},
             "sizes": res}
