@@ -165,6 +165,11 @@ def load_library(build_if_missing: bool = True, profile: str = None) -> C.CDLL:
         if not build_if_missing:
             raise LiveCCNativeError(f"{path} is missing (run `python -m livecc_b200.build`)")
         _build.build()
+    elif build_if_missing:
+        try:
+            _build.build()              # a full library older than its sources is brought up to date (a no-op otherwise)
+        except (RuntimeError, OSError):
+            pass                        # no compiler or a read-only tree: the library that is there serves
     lib = C.CDLL(str(path))
     lib.lcc_abi_version.restype = C.c_int
     if lib.lcc_abi_version() != ABI_VERSION:

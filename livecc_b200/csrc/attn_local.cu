@@ -118,6 +118,138 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_kernel(const float* __res
     }
 }
 
+// Few rows over many keys (decode steps of plain causal attention, where the window is the whole sequence and, in a
+// replayed step, only the device knows its length): one CTA per (row, head, split). The CTA walks key tiles split,
+// split + n_splits, ... of kSplitKeys keys each (so any length works with any grid; the grid only sets the parallelism), keeps
+// the running (max, sum, output) over its tiles, and leaves them in the workspace; the CTA that arrives last at the
+// (row, head) counter merges the splits with the sink's term, applies the gate and writes the row. The counter goes back to
+// zero for the next launch.
+constexpr int kSplitKeys = 256, kSplitMaxOut = 4;   // output channels per thread: DV <= 128 * kSplitMaxOut
+// The arrival counters take a fixed area at the head of the workspace, whatever the row and head counts of a call: partials
+// of one call must never lie where another call (a layer with other sizes) keeps its counters.
+constexpr int kSplitMaxHeads = 512, kSplitCounters = (kAttnTiledMin - 1) * kSplitMaxHeads;
+template <typename T> struct RowVec;
+template <> struct RowVec<bf16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[8]) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p);
+        const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+    }
+};
+template <> struct RowVec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 u = *reinterpret_cast<const float4*>(p);
+        v[0] = u.x; v[1] = u.y; v[2] = u.z; v[3] = u.w;
+    }
+};
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict__ q, const T* __restrict__ k_pages,
+                                                         const T* __restrict__ v_pages, const int* __restrict__ page_table,
+                                                         int page_size, const T* __restrict__ gate, int ld_gate,
+                                                         T* __restrict__ out, int ld_out, int S, int Hq, int G, int D, int DV,
+                                                         float scale, SeqPos pos, const float* __restrict__ sink, int ld_v,
+                                                         float* __restrict__ part, int* __restrict__ counters) {
+    if (seq_done(pos)) return;
+    extern __shared__ float sm[];
+    __shared__ float red[32];
+    __shared__ float redm[4];
+    __shared__ int last_flag;
+    float* sq = sm;            // [D]
+    float* sc = sm + D;        // [kSplitKeys]
+    const int t = blockIdx.y, h = blockIdx.x, z = blockIdx.z, nz = gridDim.z;
+    const int g = h / (Hq / G);
+    const int nkeys = seq_past(pos, S) + t + 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) sq[i] = q[((size_t)t * Hq + h) * D + i] * scale;
+    float m = -INFINITY, l = 0.f;
+    float o[kSplitMaxOut] = {};
+    for (int k0 = z * kSplitKeys; k0 < nkeys; k0 += nz * kSplitKeys) {
+        const int nk = min(kSplitKeys, nkeys - k0);
+        __syncthreads();       // sq is staged; the previous tile's weights are consumed
+        float mx = -INFINITY;
+        for (int jk = warp; jk < nk; jk += 4) {
+            const int pj = k0 + jk;
+            const T* kr = k_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * D;
+            float acc = 0.f;
+            if (VEC) {
+                constexpr int V = RowVec<T>::N;
+                for (int d = lane * V; d < D; d += 32 * V) {
+                    float kv[V];
+                    RowVec<T>::load(kr + d, kv);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) acc = fmaf(sq[d + i], kv[i], acc);
+                }
+            } else {
+                for (int d = lane; d < D; d += 32) acc = fmaf(sq[d], ldf(kr + d), acc);
+            }
+            acc = warp_sum(acc);
+            if (lane == 0) sc[jk] = acc;
+            mx = fmaxf(mx, acc);
+        }
+        if (lane == 0) redm[warp] = mx;
+        __syncthreads();
+        mx = fmaxf(fmaxf(redm[0], redm[1]), fmaxf(redm[2], redm[3]));
+        const float mn = fmaxf(m, mx);
+        const float corr = expf(m - mn);            // exp(-inf) = 0 on the first tile
+        float sum = 0.f;
+        for (int jk = threadIdx.x; jk < nk; jk += blockDim.x) {
+            const float e = expf(sc[jk] - mn);
+            sc[jk] = e;
+            sum += e;
+        }
+        sum = block_sum(sum, red);                  // contains the barrier that publishes sc[]
+        l = fmaf(l, corr, sum);
+        m = mn;
+#pragma unroll
+        for (int u = 0; u < kSplitMaxOut; ++u) {
+            const int c = threadIdx.x + u * 128;
+            if (c < DV) {
+                float acc = o[u] * corr;
+                int pj = k0, pg = pj / page_size, slot = pj - pg * page_size;
+                const T* base = v_pages + ((size_t)page_table[pg] * G + g) * page_size * ld_v + c;
+                for (int jk = 0; jk < nk; ++jk) {
+                    acc = fmaf(sc[jk], ldf(base + (size_t)slot * ld_v), acc);
+                    if (++slot == page_size && jk + 1 < nk) { slot = 0; ++pg; base = v_pages + ((size_t)page_table[pg] * G + g) * page_size * ld_v + c; }
+                }
+                o[u] = acc;
+            }
+        }
+    }
+    // partials of this split: [max, sum, out[DV]]
+    float* mine = part + (((size_t)t * Hq + h) * nz + z) * (DV + 2);
+    if (threadIdx.x == 0) { mine[0] = m; mine[1] = l; }
+#pragma unroll
+    for (int u = 0; u < kSplitMaxOut; ++u) {
+        const int c = threadIdx.x + u * 128;
+        if (c < DV) mine[2 + c] = o[u];
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last_flag = atomicAdd(counters + t * Hq + h, 1) == nz - 1;
+    __syncthreads();
+    if (!last_flag) return;
+    __threadfence();
+    const float* all = part + ((size_t)t * Hq + h) * nz * (DV + 2);
+    const float sk = sink ? sink[h] : 0.f;
+    float mt = sk;
+    for (int i = 0; i < nz; ++i) mt = fmaxf(mt, __ldcg(all + (size_t)i * (DV + 2)));
+    float lt = expf(sk - mt);                       // the sink: weight in the denominator, no value
+    for (int i = 0; i < nz; ++i) lt = fmaf(__ldcg(all + (size_t)i * (DV + 2) + 1), expf(__ldcg(all + (size_t)i * (DV + 2)) - mt), lt);
+    float gv = 1.f;
+    if (gate) gv = 1.f / (1.f + expf(-ldf(gate + (size_t)t * ld_gate + h)));
+    const float f = gv / lt;
+    for (int c = threadIdx.x; c < DV; c += blockDim.x) {
+        float acc = 0.f;
+        for (int i = 0; i < nz; ++i)
+            acc = fmaf(__ldcg(all + (size_t)i * (DV + 2) + 2 + c), expf(__ldcg(all + (size_t)i * (DV + 2)) - mt), acc);
+        stf(out + (size_t)t * ld_out + (size_t)h * DV + c, acc * f);
+    }
+    if (threadIdx.x == 0) counters[t * Hq + h] = 0;
+}
+
 // Prompt portions: one CTA per (64 query rows, query head, 128 output channels). Keys are walked in tiles of 64 from the
 // start of the chunk of the tile's first row to its last row. Per key tile the CTA stages the K tile (up to 128 head
 // channels at a time) and the V tile into shared memory in the storage type with all its loads in flight together, forms
@@ -592,13 +724,44 @@ int qk_norm_kv_append(int dt, const void* proj, int ld, const float* qn_w, const
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 
+size_t attn_split_ws_floats(int rows, int Hq, int DV) {
+    return (size_t)kSplitCounters + (size_t)rows * Hq * (DV + 2) * 32;
+}
+
 int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_pages, const int* page_table,
                     int page_size, const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D,
-                    int DV, int chunk, float scale, bool tensor_cores, SeqPos pos, cudaStream_t s, const float* sink, int ld_v) {
+                    int DV, int chunk, float scale, bool tensor_cores, SeqPos pos, cudaStream_t s, const float* sink, int ld_v,
+                    float* split_ws, size_t split_ws_floats, int key_hint) {
     if (!q || !k_pages || !v_pages || !page_table || !out || S < 1 || Hq < 1 || G < 1 || Hq % G || D < 1 || DV < 1)
         return -2;
     if (ld_v <= 0) ld_v = DV;
     if (ld_v < DV) return -2;
+    // few rows of plain causal attention over a long or device-known window: key splits across CTAs
+    const int keys_est = pos.kv_len ? std::max(key_hint, pos.past + S) : pos.past + S;
+    if (chunk <= 0 && S < kAttnTiledMin && split_ws && DV <= 128 * kSplitMaxOut && Hq <= kSplitMaxHeads &&
+        (pos.kv_len || keys_est > 2 * kSplitKeys)) {
+        const size_t per = (size_t)S * Hq * (DV + 2), cnt = kSplitCounters;
+        int nz = std::min(32, std::max(1, (keys_est + kSplitKeys - 1) / kSplitKeys));
+        if (split_ws_floats > cnt) nz = (int)std::min<size_t>(nz, (split_ws_floats - cnt) / per);
+        if (split_ws_floats > cnt && nz >= 1) {
+            int* counters = reinterpret_cast<int*>(split_ws);           // zero when the workspace is bound; every launch leaves zeros
+            float* part = split_ws + cnt;
+            const size_t smem = sizeof(float) * ((size_t)D + kSplitKeys);
+            dim3 grid(Hq, S, nz);
+            count_launch();
+#define LCC_SPLIT(T, VECB)                                                                                                   \
+    attn_split_kernel<T, VECB><<<grid, 128, smem, s>>>(q, (const T*)k_pages, (const T*)v_pages, page_table, page_size, (const T*)gate,  \
+                                                       ld_gate, (T*)out, ld_out, S, Hq, G, D, DV, scale, pos, sink, ld_v, part, counters)
+            if (smem > 48 * 1024) return -3;
+            if (dt == DT_F32) {
+                if ((D % 4) == 0 && ((uintptr_t)k_pages % 16) == 0) LCC_SPLIT(float, true); else LCC_SPLIT(float, false);
+            } else {
+                if ((D % 8) == 0 && ((uintptr_t)k_pages % 16) == 0) LCC_SPLIT(bf16, true); else LCC_SPLIT(bf16, false);
+            }
+#undef LCC_SPLIT
+            return cudaGetLastError() == cudaSuccess ? 0 : -100;
+        }
+    }
     // The one-CTA-per-row kernel keeps one score per key of the longest window a row of this call can have in shared memory.
     // Windows that do not fit (or whose length only the device knows, in a replayed step without chunks) go to the tiled
     // kernels, which walk the keys in tiles and take any row count.

@@ -72,7 +72,7 @@ constexpr int kMoeTile = 128;        // row tile of the grouped tensor-core GEMM
 constexpr int kMoeTcMinRows = 256;   // routed rows (tokens x top) from which the experts run on the tensor cores
 
 struct WsLayout {
-    size_t x32, xa, proj, proj2, mid, mid2, y32, q32, f1, f2, o1, o2, xf, scan, scan_floats, xsum, moe_f, moe_i, moe_x, moe_h, moe_o, total;
+    size_t x32, xa, proj, proj2, mid, mid2, y32, q32, f1, f2, o1, o2, xf, scan, scan_floats, xsum, moe_f, moe_i, moe_x, moe_h, moe_o, split, split_floats, total;
     int moe_rows;         // rows of the expert-sorted buffers: top per token, every list padded to a whole 128-row tile
     int w_proj, w_proj2, w_mid, w_y, w_q, w_f;
     int moe_e, moe_top;   // largest expert count and top-k of any layer (0: no routed feed-forward)
@@ -85,6 +85,7 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     int wp = 8, wp2 = 8, wm = 8, wy = 8, wq = 8, wf = 8;
     size_t scan_floats = 0;
     int moe_e = 0, moe_top = 0, moe_ff = 0, moe_rows = 0;
+    size_t split_floats = 0;   // key-split partials of few-row plain causal attention
     for (const lcc_seq_layer& l : m->layers) {
         const Dims z = dims_of(l);
         if (l.type == LCC_MIX_SSD) {
@@ -103,7 +104,10 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
         } else if (l.type == LCC_MIX_LATENT) {
             wp = std::max(wp, ld8(z.a_proj)); wm = std::max(wm, ld8(std::max(z.a_lat, z.a_o)));
             wq = std::max(wq, l.a_heads * z.a_kd);
+            split_floats = std::max(split_floats, lcc::attn_split_ws_floats(lcc::kAttnTiledMin - 1, l.a_heads, l.a_rank));
         }
+        if (l.type == LCC_MIX_PARALLEL && l.l_chunk <= 0)
+            split_floats = std::max(split_floats, lcc::attn_split_ws_floats(lcc::kAttnTiledMin - 1, l.l_heads, l.l_vdim));
         if (l.ff_kind == LCC_FF_MOE) {
             wm = std::max(wm, ld8(l.e_shared_ff));            // the shared expert's hidden row
             moe_e = std::max(moe_e, l.e_experts); moe_top = std::max(moe_top, l.e_top); moe_ff = std::max(moe_ff, ld8(l.e_ff));
@@ -139,6 +143,8 @@ WsLayout make_layout(const lcc_seq_model* m, int NT, int NW) {
     L.xf = take(nw * ld8(W) * es);
     L.scan_floats = NT >= lcc::kScanChunkedMin ? scan_floats : 0;   // a decode-only workspace has no use for it
     L.scan = take(L.scan_floats * 4);
+    L.split_floats = split_floats;
+    L.split = take(split_floats * 4);
     L.total = off;
     return L;
 }
@@ -275,6 +281,9 @@ int lcc_seq_bind_workspace(lcc_seq_model* m, void* ws, size_t ws_bytes, int max_
     if (!m || !ws) return -1;
     if (ws_bytes < make_layout(m, max_tokens, max_want).total) LCC_FAIL(m->ctx, -2, "lcc_seq_bind_workspace: buffer too small");
     m->ws = (uint8_t*)ws; m->ws_bytes = ws_bytes; m->cap_tokens = max_tokens; m->cap_want = max_want;
+    // the arrival counters at the head of the key-split area start at zero; every launch leaves them at zero
+    const WsLayout L = make_layout(m, max_tokens, max_want);
+    if (L.split_floats && cudaMemset(m->ws + L.split, 0, L.split_floats * 4) != cudaSuccess) LCC_FAIL(m->ctx, -100, "lcc_seq_bind_workspace: memset failed");
     return 0;
 }
 
@@ -312,6 +321,7 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
     float* f1 = (float*)(ws + L.f1); float* f2 = (float*)(ws + L.f2);
     uint8_t* o1 = ws + L.o1; uint8_t* o2 = ws + L.o2; uint8_t* xf = ws + L.xf;
     float* scan_ws = L.scan_floats ? (float*)(ws + L.scan) : nullptr;
+    float* split_ws = L.split_floats ? (float*)(ws + L.split) : nullptr;
     const bool hc = d.block == LCC_BLOCK_PRENORM_HC;
     const int NS = hc ? d.streams : 1;
     float* xsum = (float*)(ws + L.xsum);
@@ -402,7 +412,8 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                 const lcc_seq_entry& en = entries[e];
                 STEP(lcc::attn_chunk_sink(dt, q32 + (size_t)r0 * H * z.a_kd, en.k_pages[src], en.k_pages[src], en.page_table, page_size,
                                           proj + ((size_t)r0 * ldp + z.a_gate) * es, ldp, mid + (size_t)r0 * ldl * es, ldl, en.n_new, H, 1,
-                                          z.a_kd, l.a_rank, 0, l.a_scale, m->use_tc, pos_of(en), s, l.a_sink_f32, z.a_kd), "latent attention");
+                                          z.a_kd, l.a_rank, 0, l.a_scale, m->use_tc, pos_of(en), s, l.a_sink_f32, z.a_kd, split_ws, L.split_floats,
+                                          en.past + en.n_new), "latent attention");
                 r0 += en.n_new;
             }
             STEP(linear_heads(m, mid, ldl, l.a_rank, l.a_uv, mid2, ldo, l.a_vdim, false, H, T, l.a_vdim, l.a_rank, s), "value up-projection");
@@ -458,7 +469,8 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                      "q/k norm + cache append");
                 STEP(lcc::attn_chunk_sink(dt, q, en.k_pages[li], en.v_pages[li], en.page_table, page_size,
                                           pr + (size_t)(z.l_nq + z.l_nk + z.l_nv) * es, ldl, mid + (size_t)r0 * ldo * es, ldo, en.n_new,
-                                          l.l_heads, l.l_kv_heads, l.l_dim, l.l_vdim, l.l_chunk, l.l_scale, m->use_tc, pos, s), "chunk attention");
+                                          l.l_heads, l.l_kv_heads, l.l_dim, l.l_vdim, l.l_chunk, l.l_scale, m->use_tc, pos, s, nullptr, 0, split_ws,
+                                          L.split_floats, en.past + en.n_new), "chunk attention");
                 r0 += en.n_new;
             }
             STEP(linear(m, mid, ldo, l.l_out, nullptr, o1, W, false, T, W, z.l_o, s), "attention out-proj");

@@ -121,7 +121,14 @@ constexpr int kAttnMmaMaxDim = 256;
 int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_pages, const int* page_table,
                     int page_size, const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D,
                     int DV, int chunk, float scale, bool tensor_cores, SeqPos pos, cudaStream_t s,
-                    const float* sink = nullptr, int ld_v = 0);
+                    const float* sink = nullptr, int ld_v = 0, float* split_ws = nullptr, size_t split_ws_floats = 0,
+                    int key_hint = 0);
+// split_ws (optional, fp32, zero-filled once by the owner; attn_split_ws_floats(rows, Hq, DV) elements let every call of
+// up to `rows` rows use all its key splits): with it, calls of fewer than kAttnTiledMin rows of plain causal attention
+// (chunk <= 0) over long windows, or windows whose length only the device knows, run one CTA per (row, head, key split)
+// and merge the splits in the last CTA to arrive. key_hint: the host's estimate of the window (sets the number of splits
+// only; any length is computed correctly).
+size_t attn_split_ws_floats(int rows, int Hq, int DV);
 
 // ---- rotary.cu ----------------------------------------------------------------------------------------------------------
 // Rotary positions in the rotate-half layout: inside a head, channel i < dims/2 of the rotated block pairs with channel

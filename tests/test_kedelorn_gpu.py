@@ -180,6 +180,28 @@ def test_a_far_key_among_hundreds_at_page_borders(far_at):
     assert rel(run(m, toks, [66, 129, 298]), want) < F32_TOL
 
 
+@pytest.mark.parametrize("far_at", [0, 255, 256, 511, 512, 690])
+def test_key_splits_of_long_windows(far_at):
+    """Windows of more than 512 keys in steps of a few rows: the keys are split over several CTAs in tiles of 256 and the
+    splits are merged with the sink's term. The far key sits in the first tile, at tile edges, and in the last, ragged
+    tile; fp32 and bf16 storage; decoded alone and in portions of two and three rows; then the same through generation,
+    where only the device knows the window's length."""
+    d, tensors, A, B = _far_key_model()
+    toks = [t if t not in (A, B) else 17 for t in K.tokens(700, d["vocab"], seed=8)]
+    toks[far_at], toks[-1], toks[-3] = A, B, B
+    want = O.forward(d, tensors, toks)[0]
+    cuts = [650, 652, 655] + list(range(656, 700))
+    assert rel(run(build(d, tensors), toks, cuts), want) < F32_TOL
+    assert bf16_ok(run(build(d, tensors, "bfloat16"), toks, cuts), want)
+    if far_at == 511:
+        m = build(d, tensors)
+        new = O.greedy(d, tensors, toks[:600], 6)
+        out = m.generate(torch.tensor([toks[:600]]), max_new_tokens=6, output_logits=True)
+        assert out.sequences[0, 600:].tolist() == new
+        assert rel(torch.stack(out.logits), O.forward(d, tensors, toks[:600] + new)[0][599:605]) < F32_TOL
+        out.past_key_values.release()
+
+
 def test_a_key_far_back_in_the_retention_state_is_still_seen():
     """Retention layers only, decays close to one: the logits at the end depend on the first token through the carried
     state alone, 150 tokens and 110 decode steps later."""
