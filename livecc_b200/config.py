@@ -181,9 +181,10 @@ class RotaryConfig:
     scaling: dict = None
 
     @staticmethod
-    def from_json(d: dict) -> "RotaryConfig":
+    def from_json(d: dict, dims: int = 0) -> "RotaryConfig":
+        """`dims` is the default when the dictionary names none (the rotated part of a latent-attention head)."""
         sc = d.get("scaling")
-        return RotaryConfig(dims=int(d["dims"]), base=float(d["base"]),
+        return RotaryConfig(dims=int(d.get("dims", dims)), base=float(d["base"]),
                             scaling={k: float(sc[k]) for k in ("factor", "original", "fast", "slow")} if sc else None)
 
     def to_json(self) -> dict:
@@ -300,7 +301,7 @@ class SeqModelConfig:
             mx, mlp = L["mixer"], L.get("mlp")
             ff, moe = 0, None
             if mlp is not None:
-                kind = mlp.get("kind", "dense")
+                kind = mlp.get("kind", "moe" if "router" in mlp else "dense")
                 if kind == "dense":
                     ff = int(mlp["ff"])
                 elif kind == "moe":
@@ -318,7 +319,7 @@ class SeqModelConfig:
                 src = mx.get("kv_from")
                 layers.append(SeqLayerConfig("latent_attention", ff=ff, moe=moe, latent=LatentAttnConfig(
                     heads=int(mx["heads"]), dim=int(mx["dim"]), rot_dim=int(mx["rot_dim"]), vdim=int(mx.get("vdim", mx["dim"])),
-                    kv_rank=int(mx["kv_rank"]), scale=float(mx["scale"]), rot=RotaryConfig.from_json(mx["rot"]),
+                    kv_rank=int(mx["kv_rank"]), scale=float(mx["scale"]), rot=RotaryConfig.from_json(mx["rot"], int(mx["rot_dim"])),
                     kv_from=-1 if src is None else int(src))))
             elif L["type"] == "mamba2":
                 layers.append(SeqLayerConfig("mamba2", ssd=SsdMixerConfig(

@@ -22,7 +22,8 @@ template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = _
 __device__ __forceinline__ int seq_past(const SeqPos& p) { return p.kv_len ? *p.kv_len : p.past; }
 __device__ __forceinline__ bool seq_done(const SeqPos& p) { return p.finished && *p.finished; }
 
-// One CTA per new row.
+// gridDim.y CTAs per new row: all of them share the rotation of the query heads; the first one also norms the latent and
+// fills the cache row.
 template <typename T>
 __global__ void __launch_bounds__(256) latent_kv_append_kernel(const T* __restrict__ proj, int ld, int has_kv,
                                                                const float* __restrict__ norm_w, float eps,
@@ -38,7 +39,7 @@ __global__ void __launch_bounds__(256) latent_kv_append_kernel(const T* __restri
     const T* row = proj + (size_t)t * ld;
     const int half = DR / 2, QH = D + DR, nq = H * QH, KD = R + DR;
     // rotated query part of every head -> q_out[t, h, R + j]
-    for (int i = threadIdx.x; i < H * DR; i += blockDim.x) {
+    for (int i = threadIdx.x + blockIdx.y * blockDim.x; i < H * DR; i += blockDim.x * gridDim.y) {
         const int h = i / DR, r = i % DR;
         const int j = r < half ? r : r - half;
         const float ang = p * inv_freq[j];
@@ -47,7 +48,7 @@ __global__ void __launch_bounds__(256) latent_kv_append_kernel(const T* __restri
         const float v = ldf(qr + r), other = ldf(qr + (r < half ? r + half : r - half));
         q_out[((size_t)t * H + h) * KD + R + r] = r < half ? v * c - other * s : v * c + other * s;
     }
-    if (!has_kv) return;
+    if (!has_kv || blockIdx.y != 0) return;
     const T* lat = row + nq;
     float ss = 0.f;
     for (int i = threadIdx.x; i < R; i += blockDim.x) { const float v = ldf(lat + i); ss = fmaf(v, v, ss); }
@@ -72,11 +73,12 @@ int latent_kv_append(int dt, const void* proj, int ld, int has_kv, const float* 
     if (!proj || !inv_freq || !q_out || S < 1 || H < 1 || D < 0 || DR < 2 || (DR & 1) || R < 1) return -2;
     if (has_kv && (!norm_w || !k_pages || !page_table || page_size < 1)) return -2;
     count_launch();
+    const dim3 S_grid(S, S < 32 ? 4 : 1);
     if (dt == DT_F32)
-        latent_kv_append_kernel<float><<<S, 256, 0, s>>>((const float*)proj, ld, has_kv, norm_w, eps, inv_freq, mag, q_out,
+        latent_kv_append_kernel<float><<<S_grid, 256, 0, s>>>((const float*)proj, ld, has_kv, norm_w, eps, inv_freq, mag, q_out,
                                                          (float*)k_pages, page_table, page_size, H, D, DR, R, pos);
     else
-        latent_kv_append_kernel<bf16><<<S, 256, 0, s>>>((const bf16*)proj, ld, has_kv, norm_w, eps, inv_freq, mag, q_out,
+        latent_kv_append_kernel<bf16><<<S_grid, 256, 0, s>>>((const bf16*)proj, ld, has_kv, norm_w, eps, inv_freq, mag, q_out,
                                                         (bf16*)k_pages, page_table, page_size, H, D, DR, R, pos);
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }

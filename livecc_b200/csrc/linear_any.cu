@@ -25,6 +25,7 @@ struct Grp {
     const int* row_off;
     const int* a_rows;
     int act;
+    int compact;   // few-row kernel with lists: blockIdx.y counts the non-empty lists of `compact` groups (0: blockIdx.y is the group)
 };
 __device__ __forceinline__ float act_of(float v, int act) {
     if (act == ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
@@ -114,14 +115,21 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = (blockIdx.x * (blockDim.x >> 5) + warp) * WR;
     if (n0 >= N) return;
-    int row0 = 0;
+    int row0 = 0, z = blockIdx.y;
     if (g.row_off) {
-        row0 = g.row_off[blockIdx.y];
-        M_all = g.row_off[blockIdx.y + 1] - row0;
+        if (g.compact) {
+            // a decode step routes a handful of rows to a handful of lists: the grid has one y per possible non-empty list
+            int seen = -1;
+            for (z = 0; z < g.compact; ++z)
+                if (g.row_off[z + 1] > g.row_off[z] && ++seen == (int)blockIdx.y) break;
+            if (z == g.compact) return;
+        }
+        row0 = g.row_off[z];
+        M_all = g.row_off[z + 1] - row0;
     }
-    const T* A0 = A + blockIdx.y * g.a_stride;
-    W += blockIdx.y * g.w_stride;
-    TC* C0 = C + blockIdx.y * g.c_stride + (size_t)row0 * ldc;
+    const T* A0 = A + z * g.a_stride;
+    W += z * g.w_stride;
+    TC* C0 = C + z * g.c_stride + (size_t)row0 * ldc;
     const int* arow = g.a_rows ? g.a_rows + row0 : nullptr;
     if (!arow) A0 += (size_t)row0 * lda;
     // a group with more than kRowsMax rows walks them in blocks (the weights come from L2 after the first block); a row's
@@ -197,15 +205,17 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const T* __restrict__ 
 
 template <typename T, typename TC>
 int launch_linear(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N, int K,
-                  cudaStream_t s, int groups = 1, Grp g = Grp{0, 0, 0, nullptr, nullptr, ACT_NONE}, int M_total = 0) {
+                  cudaStream_t s, int groups = 1, Grp g = Grp{0, 0, 0, nullptr, nullptr, ACT_NONE, 0}, int M_total = 0) {
     // lists: the row kernel while all groups together have few rows (a decode step routes `top` rows per sequence)
     if (g.row_off ? M_total <= 8 * kRowsMax : M <= kRowsMax) {
         constexpr int V = Vec16<T>::N;
         const bool vec = (K % V) == 0 && (lda % V) == 0 && (ldw % V) == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0 &&
                          (g.a_stride % V) == 0 && (g.w_stride % V) == 0;
+        int grid_y = groups;
+        if (g.row_off && M_total < groups) { g.compact = groups; grid_y = M_total; }
         count_launch();
 #define LCC_ROWS(VECB, WRN, WARPS)                                                                                         \
-    linear_rows_kernel<T, TC, VECB, WRN><<<dim3((N + WARPS * WRN - 1) / (WARPS * WRN), groups), WARPS * 32, 0, s>>>(            \
+    linear_rows_kernel<T, TC, VECB, WRN><<<dim3((N + WARPS * WRN - 1) / (WARPS * WRN), grid_y), WARPS * 32, 0, s>>>(            \
         (const T*)A, lda, (const T*)W, ldw, bias, (TC*)C, ldc, M, N, K, g)
         if (N >= 8192) {
             if (vec) LCC_ROWS(true, 2, 8); else LCC_ROWS(false, 2, 8);
@@ -235,7 +245,7 @@ int linear_grouped(const GroupedLinear& q, cudaStream_t s) {
     if (!q.A || !q.W || !q.C || q.groups < 1 || q.groups > 65535 || q.M < 1 || q.N < 1 || q.K < 1 || q.lda < q.K || q.ldw < q.K ||
         q.ldc < q.N || (q.a_rows && !q.row_off))
         return -2;
-    const Grp g{q.a_stride, q.w_stride, q.c_stride, q.row_off, q.a_rows, q.act};
+    const Grp g{q.a_stride, q.w_stride, q.c_stride, q.row_off, q.a_rows, q.act, 0};
     const int mt = q.row_off ? (q.M_total > 0 ? q.M_total : q.M * q.groups) : 0;
     if (q.dt == DT_F32) return launch_linear<float, float>(q.A, q.lda, q.W, q.ldw, nullptr, q.C, q.ldc, q.M, q.N, q.K, s, q.groups, g, mt);
     if (q.c_f32) return launch_linear<bf16, float>(q.A, q.lda, q.W, q.ldw, nullptr, q.C, q.ldc, q.M, q.N, q.K, s, q.groups, g, mt);

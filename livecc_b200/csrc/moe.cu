@@ -22,13 +22,10 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-
 // pick the experts in descending order of choice score. The arrival number inside an expert comes from an atomic
 // counter: it decides only where the row sits in the expert's list, never a value.
 constexpr int kMaxExpertsPerLane = 16;   // experts <= 512
-__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ correction,
-                                                        int E, int top, float scale, int* __restrict__ sel,
-                                                        float* __restrict__ weight, float* __restrict__ shared_gate,
-                                                        int* __restrict__ counts, int* __restrict__ rank, int S) {
-    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (r >= S) return;
-    const float* z = logits + (size_t)r * ld;
+// The choice for one row by one warp; lane 0 returns the k-th expert and its score through `emit`.
+template <typename Emit>
+__device__ __forceinline__ void route_row(const float* __restrict__ z, const float* __restrict__ correction, int E, int top, Emit emit) {
+    const int lane = threadIdx.x & 31;
     float sc[kMaxExpertsPerLane], ch[kMaxExpertsPerLane];
 #pragma unroll
     for (int i = 0; i < kMaxExpertsPerLane; ++i) {
@@ -53,13 +50,59 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 #pragma unroll
         for (int i = 0; i < kMaxExpertsPerLane; ++i)
             if (lane + 32 * i == be) ch[i] = -INFINITY;
-        if (lane == 0) {
+        if (lane == 0) emit(k, be, bs);
+    }
+}
+
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ correction,
+                                                        int E, int top, float scale, int* __restrict__ sel,
+                                                        float* __restrict__ weight, float* __restrict__ shared_gate,
+                                                        int* __restrict__ counts, int* __restrict__ rank, int S) {
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= S) return;
+    const float* z = logits + (size_t)r * ld;
+    route_row(z, correction, E, top, [&](int k, int be, float bs) {
+        sel[(size_t)r * top + k] = be;
+        weight[(size_t)r * top + k] = bs * scale;
+        rank[(size_t)r * top + k] = atomicAdd(counts + be, 1);
+    });
+    if (shared_gate && lane == 0) shared_gate[r] = sigmoid_f(z[E]);
+}
+
+// Few rows (a decode step): one CTA routes every row, counts the lists in shared memory and writes the dense row lists,
+// which takes the counter reset, the choice and the list kernel of the general route into one launch.
+constexpr int kSmallRouteItems = 1024, kSmallRouteExperts = 512;
+__global__ void __launch_bounds__(256) moe_route_small_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ correction,
+                                                              int E, int top, float scale, int* __restrict__ sel,
+                                                              float* __restrict__ weight, float* __restrict__ shared_gate,
+                                                              int* __restrict__ row_off, int* __restrict__ pos,
+                                                              int* __restrict__ src_row, int S) {
+    __shared__ int cnt[kSmallRouteExperts + 1];
+    __shared__ int rk[kSmallRouteItems];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int r = warp; r < S; r += (blockDim.x >> 5)) {
+        const float* z = logits + (size_t)r * ld;
+        route_row(z, correction, E, top, [&](int k, int be, float bs) {
             sel[(size_t)r * top + k] = be;
             weight[(size_t)r * top + k] = bs * scale;
-            rank[(size_t)r * top + k] = atomicAdd(counts + be, 1);
-        }
+            rk[r * top + k] = atomicAdd(&cnt[be], 1);
+        });
+        if (shared_gate && lane == 0) shared_gate[r] = sigmoid_f(z[E]);
     }
-    if (shared_gate && lane == 0) shared_gate[r] = sigmoid_f(z[E]);
+    __syncthreads();
+    if (threadIdx.x == 0) {         // exclusive prefix sum in place
+        int o = 0;
+        for (int e = 0; e <= E; ++e) { const int c = cnt[e]; cnt[e] = o; o += c; }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) row_off[e] = cnt[e];
+    for (int i = threadIdx.x; i < S * top; i += blockDim.x) {
+        const int p = cnt[sel[i]] + rk[i];      // sel[i] was written by a thread of this CTA before the barriers
+        pos[i] = p;
+        src_row[p] = i / top;
+    }
 }
 
 // Lists padded to whole tiles of `pad` rows (pad = 1: dense lists): list e starts at the sum of the padded counts before it.
@@ -124,6 +167,16 @@ int moe_route(const float* logits, int ld, const float* correction, int E, int t
         return -2;
     count_launch();
     moe_route_kernel<<<(S + 3) / 4, 128, 0, s>>>(logits, ld, correction, E, top, scale, sel, weight, shared_gate, counts, rank, S);
+    return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+int moe_route_small(const float* logits, int ld, const float* correction, int E, int top, float scale, int* sel, float* weight,
+                    float* shared_gate, int* row_off, int* pos, int* src_row, int S, cudaStream_t s) {
+    if (!logits || !correction || !sel || !weight || !row_off || !pos || !src_row || S < 1 || E < 1 || E > kSmallRouteExperts ||
+        top < 1 || top > E || S * top > kSmallRouteItems || ld < E + (shared_gate ? 1 : 0))
+        return -2;
+    count_launch();
+    moe_route_small_kernel<<<1, 256, 0, s>>>(logits, ld, correction, E, top, scale, sel, weight, shared_gate, row_off, pos, src_row, S);
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 

@@ -18,7 +18,8 @@ __device__ __forceinline__ bool seq_done(const SeqPos& p) { return p.finished &&
 
 struct Segs { RotarySegment s[4]; int n; };
 
-// One CTA per row; threads walk the output channels of every segment.
+// gridDim.y CTAs per row (several when the call has few rows, so that a decode step's single row is not one CTA's serial
+// walk); together their threads walk the output channels of every segment.
 template <typename T>
 __global__ void __launch_bounds__(256) rotary_pack_kernel(const T* __restrict__ in, int ld_in, float* __restrict__ out, int ld_out,
                                                           Segs segs, const float* __restrict__ inv_freq, float mag,
@@ -32,7 +33,7 @@ __global__ void __launch_bounds__(256) rotary_pack_kernel(const T* __restrict__ 
     for (int si = 0; si < segs.n; ++si) {
         const RotarySegment sg = segs.s[si];
         const int n = sg.heads * sg.dim, half = sg.rot_dims / 2;
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        for (int i = threadIdx.x + blockIdx.y * blockDim.x; i < n; i += blockDim.x * gridDim.y) {
             const int d = i % sg.dim, hb = i - d;
             const int r = d - sg.rot_off;
             float v = ldf(row + sg.col_in + i);
@@ -46,7 +47,7 @@ __global__ void __launch_bounds__(256) rotary_pack_kernel(const T* __restrict__ 
             orow[sg.col_out + i] = v * sg.scale;
         }
     }
-    if (fill_out)
+    if (fill_out && blockIdx.y == 0)
         for (int i = threadIdx.x; i < fill_n; i += blockDim.x) fill_out[(size_t)t * fill_n + i] = fill[i];
 }
 
@@ -65,10 +66,11 @@ int rotary_pack_f32(int dt, const void* in, int ld_in, float* out, int ld_out, c
             return -2;
     }
     count_launch();
+    const dim3 S_grid(S, S < 32 ? 8 : 1);
     if (dt == DT_F32)
-        rotary_pack_kernel<float><<<S, 256, 0, s>>>((const float*)in, ld_in, out, ld_out, g, inv_freq, mag, fill, fill_out, fill_n, pos);
+        rotary_pack_kernel<float><<<S_grid, 256, 0, s>>>((const float*)in, ld_in, out, ld_out, g, inv_freq, mag, fill, fill_out, fill_n, pos);
     else
-        rotary_pack_kernel<bf16><<<S, 256, 0, s>>>((const bf16*)in, ld_in, out, ld_out, g, inv_freq, mag, fill, fill_out, fill_n, pos);
+        rotary_pack_kernel<bf16><<<S_grid, 256, 0, s>>>((const bf16*)in, ld_in, out, ld_out, g, inv_freq, mag, fill, fill_out, fill_n, pos);
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 

@@ -327,11 +327,15 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
     float* xsum = (float*)(ws + L.xsum);
     // pre-norm blocks: the sublayer output that the next boundary kernel folds into the streams
     const float* pend_hc = nullptr;
+    lcc::MoeCombine pend_mc{};      // set when that sublayer was a routed feed-forward: its combine runs inside the boundary
+    bool pend_is_mc = false;
     // boundary between sublayers of a pre-norm block: fold the finished sublayer's output (o1) into the streams, read and
     // norm for the next one (next_hc / next_w; null at the end of the model), optionally emit the sum of the streams
     auto boundary = [&](const float* next_hc, const float* next_w, float* sum_out) -> int {
-        const int rc = lcc::hyper_boundary(dt, x32, NS, pend_hc ? ws + L.o1 : nullptr, W, pend_hc, next_hc, next_w, d.eps, xa, sum_out, T, W, s);
+        const int rc = lcc::hyper_boundary(dt, x32, NS, (pend_hc && !pend_is_mc) ? ws + L.o1 : nullptr, W, pend_hc, next_hc, next_w, d.eps, xa,
+                                           sum_out, T, W, s, (pend_hc && pend_is_mc) ? &pend_mc : nullptr);
         pend_hc = nullptr;
+        pend_is_mc = false;
         return rc;
     };
     auto pos_of = [&](const lcc_seq_entry& e) {
@@ -525,10 +529,15 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             const int rows_max = T * K + E * (kMoeTile - 1), n_tiles = (rows_max + kMoeTile - 1) / kMoeTile;
             // router logits (and the shared expert's gate logit) accumulate in fp32 from the normed row
             STEP(linear(m, xa, W, l.e_router, nullptr, logit, lde, true, T, E + (shared ? 1 : 0), W, s), "router");
-            if (cudaMemsetAsync(counts, 0, sizeof(int) * E, s) != cudaSuccess) LCC_FAIL(m->ctx, -100, "router counters");
-            if (tc && cudaMemsetAsync(src_row, 0xff, sizeof(int) * (size_t)n_tiles * kMoeTile, s) != cudaSuccess) LCC_FAIL(m->ctx, -100, "row lists");
-            STEP(lcc::moe_route(logit, lde, l.e_correction_f32, E, K, l.e_scale, sel, wsel, shared ? sgate : nullptr, counts, rank, T, s), "expert choice");
-            STEP(lcc::moe_index(sel, rank, counts, E, K, tc ? kMoeTile : 1, row_off, posn, src_row, tc ? tile_group : nullptr, n_tiles, T, s), "expert row lists");
+            if (!tc && T * K <= 256 && E <= 512) {
+                STEP(lcc::moe_route_small(logit, lde, l.e_correction_f32, E, K, l.e_scale, sel, wsel, shared ? sgate : nullptr, row_off, posn,
+                                          src_row, T, s), "expert choice + row lists");
+            } else {
+                if (cudaMemsetAsync(counts, 0, sizeof(int) * E, s) != cudaSuccess) LCC_FAIL(m->ctx, -100, "router counters");
+                if (tc && cudaMemsetAsync(src_row, 0xff, sizeof(int) * (size_t)n_tiles * kMoeTile, s) != cudaSuccess) LCC_FAIL(m->ctx, -100, "row lists");
+                STEP(lcc::moe_route(logit, lde, l.e_correction_f32, E, K, l.e_scale, sel, wsel, shared ? sgate : nullptr, counts, rank, T, s), "expert choice");
+                STEP(lcc::moe_index(sel, rank, counts, E, K, tc ? kMoeTile : 1, row_off, posn, src_row, tc ? tile_group : nullptr, n_tiles, T, s), "expert row lists");
+            }
             if (tc) {
                 STEP(lcc::moe_gather_rows(dt, xa, W, src_row, ex, ldw8, n_tiles * kMoeTile, W, s), "expert row gather");
                 lcc::GemmArgs a;
@@ -554,7 +563,12 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                 STEP(linear(m, xa, W, l.e_shared_up, nullptr, mid2, lds, false, T, l.e_shared_ff, W, s, nullptr, lcc::ACT_RELU2), "shared expert up");
                 STEP(linear(m, mid2, lds, l.e_shared_down, nullptr, o2, W, false, T, W, l.e_shared_ff, s), "shared expert down");
             }
-            STEP(lcc::moe_combine(dt, eo, ldw8, posn, wsel, K, shared ? o2 : nullptr, W, sgate, o1, W, T, W, s), "expert combine");
+            if (hc) {   // the weighted sum of the experts' rows is formed by the boundary kernel that folds it into the streams
+                pend_mc = lcc::MoeCombine{eo, ldw8, posn, wsel, K, shared ? o2 : nullptr, W, sgate};
+                pend_is_mc = true;
+            } else {
+                STEP(lcc::moe_combine(dt, eo, ldw8, posn, wsel, K, shared ? o2 : nullptr, W, sgate, o1, W, T, W, s), "expert combine");
+            }
         } else if (l.ff > 0) {
             const int ldg = ld8(2 * l.ff), ldf = ld8(l.ff);
             STEP(linear(m, xa, W, l.ff_in, nullptr, proj, ldg, false, T, 2 * l.ff, W, s), "feed-forward in");

@@ -158,8 +158,14 @@ int latent_kv_append(int dt, const void* proj, int ld, int has_kv, const float* 
 //   (2) if w:  u = sum_s in[s] x_s;  xa = u / sqrt(mean(u^2) + eps) * w   (storage dt; w is the full weight)
 //   (3) if sum_out: sum_out = sum_s x_s  (fp32 [S, W])
 // prev: fp32 [in: n | out: n | mix: n*n] of the sublayer that produced y; next: the same block of the sublayer that reads xa.
+// mc (instead of y): the finished sublayer is a routed feed-forward whose output row is formed here,
+//   y[r] = sum_k weight[r, k] * eo[pos[r, k]] + gate[r] * so[r]   (in fp32; moe_combine as part of the boundary).
+struct MoeCombine {
+    const void* eo; int ld_eo; const int* pos; const float* weight; int top;
+    const void* so; int ld_so; const float* gate;      // so null: no shared expert
+};
 int hyper_boundary(int dt, float* xs, int n, const void* y, int ld_y, const float* prev, const float* next, const float* w,
-                   float eps, void* xa, float* sum_out, int S, int W, cudaStream_t s);
+                   float eps, void* xa, float* sum_out, int S, int W, cudaStream_t s, const MoeCombine* mc = nullptr);
 
 // ---- moe.cu -------------------------------------------------------------------------------------------------------------
 // Router of a mixture of experts. logits fp32 [S, ld] (E expert logits, then optionally the shared expert's gate logit at
@@ -169,6 +175,11 @@ int hyper_boundary(int dt, float* xs, int n, const void* y, int ld_y, const floa
 // receives the number of rows per expert; rank int32 [S, top] = the row's arrival number inside its expert.
 int moe_route(const float* logits, int ld, const float* correction, int E, int top, float scale, int* sel, float* weight,
               float* shared_gate, int* counts, int* rank, int S, cudaStream_t s);
+// moe_route and moe_index (dense lists) in one launch of one CTA, for calls of up to kMoeSmallItems (row, choice) pairs; it
+// needs no counters.
+constexpr int kMoeSmallItems = 1024;
+int moe_route_small(const float* logits, int ld, const float* correction, int E, int top, float scale, int* sel, float* weight,
+                    float* shared_gate, int* row_off, int* pos, int* src_row, int S, cudaStream_t s);
 // Expert-sorted row lists. Each list is padded to a multiple of `pad` rows (1: dense). row_off int32 [E+1] = start of every
 // list (row_off[E] = total); pos[r, k] = row_off[sel] + rank = the row's place; src_row[pos] = r (entries of padding rows
 // are not written: fill src_row with -1 first when pad > 1). tile_group (optional, int32 [n_tiles]): the list that owns

@@ -234,10 +234,11 @@ def test_long_prompts_cross_many_blocks_of_the_recurrence_and_key_tiles():
     assert rel(run(m, toks, [100, 131, 133, 260, 292]), want_lg) < F32_TOL
 
 
-@pytest.mark.parametrize("rank,rot_dim,vdim", [(136, 8, 24), (60, 12, 140), (248, 8, 16)])
+@pytest.mark.parametrize("rank,rot_dim,vdim", [(136, 8, 24), (60, 12, 140), (248, 8, 16), (300, 10, 8)])
 def test_latents_wider_than_one_tile(rank, rot_dim, vdim):
     """Cache rows of 144, 72 and 256 channels (several channel steps per key tile, two output tiles for a 136- or
-    248-channel latent), in fp32 and in bf16 on the tensor-core attention."""
+    248-channel latent), in fp32 and in bf16 on the tensor-core attention; rows of 310 channels are beyond its head size
+    and run on the CUDA-core tiles in both storage types."""
     layers = [K.lat(heads=2, dim=12, rot_dim=rot_dim, vdim=vdim, kv_rank=rank, scale=0.2, scaling=None, mlp=None),
               K.ret(heads=2, dim=70, vdim=67, decay=(0.9, 0.99), rot_dims=34, mlp=None)]
     d = K.config(layers, width=32, vocab=64)
