@@ -448,7 +448,7 @@ int launch_attn_tiled(const float* q, const void* k_pages, const void* v_pages, 
 // buffered asynchronous copies); scores and the product with V are mma.sync m16n8k16 with
 // fp32 accumulators, the softmax (running max and sum started at the sink's term, exp in fp32) works on the accumulator
 // fragments, and the weights go to the second product as bf16 A fragments straight from registers.
-constexpr int MQ = 64, MK = 64, MVW = 128, MLV = MVW + 8;
+constexpr int MQ = 64, MK = 64;
 
 // rows that are not 16-byte aligned: element-wise staging
 template <typename RowPtr>
@@ -460,7 +460,7 @@ __device__ __forceinline__ void stage_bf16_rows(bf16* dst, int ld_dst, int ncp, 
     }
 }
 
-template <bool VEC8, int KH>
+template <bool VEC8, int KH, int NV>
 __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_pages,
                                                                   const bf16* __restrict__ v_pages, const int* __restrict__ page_table,
                                                                   int page_size, const bf16* __restrict__ gate, int ld_gate,
@@ -469,6 +469,8 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
                                                                   const float* __restrict__ sink, int ld_v) {
     if (seq_done(pos)) return;
     extern __shared__ __align__(16) uint8_t smem_attn[];
+    // NV output tiles of 128 channels per CTA (NV = 2: values of up to 256 channels against one pass over the scores)
+    constexpr int MVW = 128 * NV, MLV = MVW + 8;
     const int Dp = (D + 15) / 16 * 16, LQ = Dp + 8;
     bf16* sQ = reinterpret_cast<bf16*>(smem_attn);     // [MQ][LQ]
     constexpr int KT = KH * MK;                         // keys per step of the CTA: one 64-key tile per group of 4 warps
@@ -500,7 +502,7 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
     float m[2] = {sk, sk};
     // per-thread partial sums; the sink's 1 is counted once per row (by one thread of the first group of warps)
     float l[2] = {(tq == 0 && kh == 0) ? 1.f : 0.f, (tq == 0 && kh == 0) ? 1.f : 0.f};
-    float o[16][4] = {};
+    float o[16 * NV][4] = {};
     // VEC8: a tile's K and V rows arrive by 16-byte asynchronous copies (zero-filled past the last key and in the padding
     // columns), all in flight together, into the buffer the previous tile does not use, while that tile is computed
     auto issue = [&](int k0, int buf) {
@@ -607,7 +609,7 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
             m[i] = mn;
         }
 #pragma unroll
-        for (int nt = 0; nt < 16; ++nt) { o[nt][0] *= corr[0]; o[nt][1] *= corr[0]; o[nt][2] *= corr[1]; o[nt][3] *= corr[1]; }
+        for (int nt = 0; nt < 16 * NV; ++nt) { o[nt][0] *= corr[0]; o[nt][1] *= corr[0]; o[nt][2] *= corr[1]; o[nt][3] *= corr[1]; }
 #pragma unroll
         for (int j2 = 0; j2 < 4; ++j2) {
             if (k0 + j2 * 16 > pl) break;              // uniform: the tile's remaining keys do not exist
@@ -617,7 +619,7 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
             a[2] = pack_bf16x2(sc[2 * j2 + 1][0], sc[2 * j2 + 1][1]);
             a[3] = pack_bf16x2(sc[2 * j2 + 1][2], sc[2 * j2 + 1][3]);
 #pragma unroll
-            for (int ntp = 0; ntp < 8; ++ntp) {
+            for (int ntp = 0; ntp < 8 * NV; ++ntp) {
                 if (ntp * 16 < DVp) {
                     uint32_t b0, b1, b2, b3;
                     ldmatrix_x4_trans(b0, b1, b2, b3, sV + (size_t)(j2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * MLV + ntp * 16 + (lane >> 4) * 8);
@@ -627,7 +629,8 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
             }
         }
     }
-    if (KH > 1) {
+    static_assert(KH == 1 || NV == 1, "two groups of warps exchange one 128-channel tile");
+    if (KH > 1 && NV == 1) {
         // the second group hands its (max, partial sum, unnormalised output) to the first through the tile buffers (K and V
         // buffers are contiguous; every asynchronous copy was waited for in the last step)
         float* xch = reinterpret_cast<float*>(sK0);
@@ -668,7 +671,7 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
         if (gate) gv = 1.f / (1.f + expf(-ldf(gate + (size_t)t * ld_gate + h)));
         const float f = gv / lt;
 #pragma unroll
-        for (int nt = 0; nt < 16; ++nt)
+        for (int nt = 0; nt < 16 * NV; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int col = nt * 8 + 2 * tq + e;
@@ -680,28 +683,32 @@ __global__ void __launch_bounds__(128 * KH) attn_chunk_sink_mma_kernel(const flo
 int launch_attn_mma(const float* q, const void* k_pages, const void* v_pages, const int* page_table, int page_size,
                     const void* gate, int ld_gate, void* out, int ld_out, int S, int Hq, int G, int D, int DV, int chunk,
                     float scale, SeqPos pos, cudaStream_t s, const float* sink, int ld_v) {
-    static SmemAttrOnce once82, once81, once1;
+    static SmemAttrOnce once82, once81, once1, once81w, once1w;
     const int Dp = (D + 15) / 16 * 16;
     // 16-byte copies need every K and V row (and the output-channel slice) to start on a 16-byte boundary
     const bool vec8 = (D % 8) == 0 && (DV % 8) == 0 && (ld_v % 8) == 0 && ((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0;
     // two groups of warps (two key tiles per step) when four tiles of K and V fit beside Q; the exchange area of the final
     // merge (68 floats per thread of a group, 34 KB) lies over the K and V buffers, whose V part alone is 68 KB
-    const bool two = vec8 && Dp <= 128;
-    const int nbuf = vec8 ? 2 : 1, kh = two ? 2 : 1;
+    // values wider than 128 channels: two output tiles per CTA against one pass over the scores (one group of warps)
+    const bool wide = DV > 128;
+    const bool two = vec8 && Dp <= 128 && !wide;
+    const int nbuf = vec8 ? 2 : 1, kh = two ? 2 : 1, MVW = wide ? 256 : 128, MLV = MVW + 8;
     auto bytes = [&](int dp) { return ((size_t)MQ * (dp + 8) + (size_t)nbuf * kh * MK * (dp + 8 + MLV)) * sizeof(bf16); };
     const size_t smem = bytes(Dp), smem_max = bytes(two ? 128 : kAttnMmaMaxDim);
     dim3 grid(Hq, (S + MQ - 1) / MQ, (DV + MVW - 1) / MVW);
     count_launch();
-#define LCC_ATTN_MMA(ONCE, VEC, KHN)                                                                                         \
+#define LCC_ATTN_MMA(ONCE, VEC, KHN, NVN)                                                                                       \
     do {                                                                                                                     \
-        if (ensure_dyn_smem(ONCE, attn_chunk_sink_mma_kernel<VEC, KHN>, (int)smem_max)) return -100;                         \
-        attn_chunk_sink_mma_kernel<VEC, KHN><<<grid, 128 * KHN, smem, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table, \
+        if (ensure_dyn_smem(ONCE, attn_chunk_sink_mma_kernel<VEC, KHN, NVN>, (int)smem_max)) return -100;                         \
+        attn_chunk_sink_mma_kernel<VEC, KHN, NVN><<<grid, 128 * KHN, smem, s>>>(q, (const bf16*)k_pages, (const bf16*)v_pages, page_table, \
                                                                            page_size, (const bf16*)gate, ld_gate, (bf16*)out, ld_out, \
                                                                            S, Hq, G, D, DV, chunk, scale, pos, sink, ld_v);  \
     } while (0)
-    if (two) LCC_ATTN_MMA(once82, true, 2);
-    else if (vec8) LCC_ATTN_MMA(once81, true, 1);
-    else LCC_ATTN_MMA(once1, false, 1);
+    if (two) LCC_ATTN_MMA(once82, true, 2, 1);
+    else if (wide && vec8) LCC_ATTN_MMA(once81w, true, 1, 2);
+    else if (wide) LCC_ATTN_MMA(once1w, false, 1, 2);
+    else if (vec8) LCC_ATTN_MMA(once81, true, 1, 1);
+    else LCC_ATTN_MMA(once1, false, 1, 1);
 #undef LCC_ATTN_MMA
     return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
