@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(128) attn_chunk_sink_kernel(const float* __res
 // the running (max, sum, output) over its tiles, and leaves them in the workspace; the CTA that arrives last at the
 // (row, head) counter merges the splits with the sink's term, applies the gate and writes the row. The counter goes back to
 // zero for the next launch.
-constexpr int kSplitKeys = 256, kSplitMaxOut = 4;   // output channels per thread: DV <= 128 * kSplitMaxOut
+constexpr int kSplitKeys = 128, kSplitMaxOut = 4;   // output channels per thread: DV <= 128 * kSplitMaxOut
 // The arrival counters take a fixed area at the head of the workspace, whatever the row and head counts of a call: partials
 // of one call must never lie where another call (a layer with other sizes) keeps its counters.
 constexpr int kSplitMaxHeads = 512, kSplitCounters = (kAttnTiledMin - 1) * kSplitMaxHeads;
@@ -156,6 +156,7 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
     extern __shared__ float sm[];
     __shared__ float red[32];
     __shared__ float redm[4];
+    __shared__ int row_of[kSplitKeys];     // a key's row in the page pool: (page * G + g) * page_size + slot
     __shared__ int last_flag;
     float* sq = sm;            // [D]
     float* sc = sm + D;        // [kSplitKeys]
@@ -170,24 +171,45 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
         const int nk = min(kSplitKeys, nkeys - k0);
         __syncthreads();       // sq is staged; the previous tile's weights are consumed
         float mx = -INFINITY;
-        for (int jk = warp; jk < nk; jk += 4) {
-            const int pj = k0 + jk;
-            const T* kr = k_pages + (((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size) * D;
-            float acc = 0.f;
+        // a warp takes four consecutive keys at a time and has all their loads in flight before it sums
+        for (int j0 = warp * 4; j0 < nk; j0 += 16) {
+            const T* kr[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int pj = k0 + min(j0 + j, nk - 1);
+                const size_t ro = ((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size;
+                kr[j] = k_pages + ro * D;
+                if (lane == 0 && j0 + j < nk) row_of[j0 + j] = (int)ro;
+            }
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
             if (VEC) {
                 constexpr int V = RowVec<T>::N;
                 for (int d = lane * V; d < D; d += 32 * V) {
-                    float kv[V];
-                    RowVec<T>::load(kr + d, kv);
+                    float kv[4][V];
 #pragma unroll
-                    for (int i = 0; i < V; ++i) acc = fmaf(sq[d + i], kv[i], acc);
+                    for (int j = 0; j < 4; ++j) RowVec<T>::load(kr[j] + d, kv[j]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int i = 0; i < V; ++i) acc[j] = fmaf(sq[d + i], kv[j][i], acc[j]);
                 }
             } else {
-                for (int d = lane; d < D; d += 32) acc = fmaf(sq[d], ldf(kr + d), acc);
+                for (int d = lane; d < D; d += 32) {
+                    float kv[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) kv[j] = ldf(kr[j] + d);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[j] = fmaf(sq[d], kv[j], acc[j]);
+                }
             }
-            acc = warp_sum(acc);
-            if (lane == 0) sc[jk] = acc;
-            mx = fmaxf(mx, acc);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float v = warp_sum(acc[j]);
+                if (j0 + j < nk) {
+                    if (lane == 0) sc[j0 + j] = v;
+                    mx = fmaxf(mx, v);
+                }
+            }
         }
         if (lane == 0) redm[warp] = mx;
         __syncthreads();
@@ -208,11 +230,14 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
             const int c = threadIdx.x + u * 128;
             if (c < DV) {
                 float acc = o[u] * corr;
-                int pj = k0, pg = pj / page_size, slot = pj - pg * page_size;
-                const T* base = v_pages + ((size_t)page_table[pg] * G + g) * page_size * ld_v + c;
-                for (int jk = 0; jk < nk; ++jk) {
-                    acc = fmaf(sc[jk], ldf(base + (size_t)slot * ld_v), acc);
-                    if (++slot == page_size && jk + 1 < nk) { slot = 0; ++pg; base = v_pages + ((size_t)page_table[pg] * G + g) * page_size * ld_v + c; }
+                // eight rows' loads in flight at a time; the rows' places in the pages were left by the score pass
+                for (int j0 = 0; j0 < nk; j0 += 8) {
+                    float vv[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) vv[j] = ldf(v_pages + (size_t)row_of[min(j0 + j, nk - 1)] * ld_v + c);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (j0 + j < nk) acc = fmaf(sc[j0 + j], vv[j], acc);
                 }
                 o[u] = acc;
             }
