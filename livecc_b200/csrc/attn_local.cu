@@ -166,7 +166,10 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int i = threadIdx.x; i < D; i += blockDim.x) sq[i] = q[((size_t)t * Hq + h) * D + i] * scale;
     float m = -INFINITY, l = 0.f;
-    float o[kSplitMaxOut] = {};
+    float o[kSplitMaxOut] = {};                      // scalar form: thread c owns channels c, c + 128, ...
+    constexpr int VN = VEC ? RowVec<T>::N : 1, NP = VEC ? 128 * kSplitMaxOut / (32 * RowVec<T>::N) : 1;
+    float ov[NP][VN] = {};                           // vector form: a warp's sum over ITS keys of 16-byte pieces lane, lane + 32, ...
+    float* osum = sc + kSplitKeys;                   // [4][DV], vector form only
     for (int k0 = z * kSplitKeys; k0 < nkeys; k0 += nz * kSplitKeys) {
         const int nk = min(kSplitKeys, nkeys - k0);
         __syncthreads();       // sq is staged; the previous tile's weights are consumed
@@ -225,6 +228,32 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
         sum = block_sum(sum, red);                  // contains the barrier that publishes sc[]
         l = fmaf(l, corr, sum);
         m = mn;
+        if constexpr (VEC) {
+            // a warp takes eight consecutive keys at a time; its lanes read 16-byte pieces of their value rows, all in flight
+            // together. The four warps' sums are added after the last tile.
+#pragma unroll
+            for (int p = 0; p < NP; ++p)
+#pragma unroll
+                for (int i = 0; i < VN; ++i) ov[p][i] *= corr;
+            for (int j0 = warp * 8; j0 < nk; j0 += 32) {
+#pragma unroll
+                for (int p = 0; p < NP; ++p) {
+                    const int c = (lane + 32 * p) * VN;
+                    if (c < DV) {
+                        float vv[8][VN];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) RowVec<T>::load(v_pages + (size_t)row_of[min(j0 + j, nk - 1)] * ld_v + c, vv[j]);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float wj = j0 + j < nk ? sc[j0 + j] : 0.f;
+#pragma unroll
+                            for (int i = 0; i < VN; ++i) ov[p][i] = fmaf(wj, vv[j][i], ov[p][i]);
+                        }
+                    }
+                }
+            }
+            continue;
+        }
 #pragma unroll
         for (int u = 0; u < kSplitMaxOut; ++u) {
             const int c = threadIdx.x + u * 128;
@@ -246,10 +275,24 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
     // partials of this split: [max, sum, out[DV]]
     float* mine = part + (((size_t)t * Hq + h) * nz + z) * (DV + 2);
     if (threadIdx.x == 0) { mine[0] = m; mine[1] = l; }
+    if constexpr (VEC) {
+        __syncthreads();                             // the last tile's weights are consumed (osum lies behind them)
 #pragma unroll
-    for (int u = 0; u < kSplitMaxOut; ++u) {
-        const int c = threadIdx.x + u * 128;
-        if (c < DV) mine[2 + c] = o[u];
+        for (int p = 0; p < NP; ++p) {
+            const int c = (lane + 32 * p) * VN;
+            if (c < DV)
+#pragma unroll
+                for (int i = 0; i < VN; ++i) osum[(size_t)warp * DV + c + i] = ov[p][i];
+        }
+        __syncthreads();
+        for (int c = threadIdx.x; c < DV; c += blockDim.x)
+            mine[2 + c] = (osum[c] + osum[DV + c]) + (osum[2 * DV + c] + osum[3 * DV + c]);
+    } else {
+#pragma unroll
+        for (int u = 0; u < kSplitMaxOut; ++u) {
+            const int c = threadIdx.x + u * 128;
+            if (c < DV) mine[2 + c] = o[u];
+        }
     }
     __threadfence();
     __syncthreads();
@@ -778,7 +821,7 @@ int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_p
         if (split_ws_floats > cnt && nz >= 1) {
             int* counters = reinterpret_cast<int*>(split_ws);           // zero when the workspace is bound; every launch leaves zeros
             float* part = split_ws + cnt;
-            const size_t smem = sizeof(float) * ((size_t)D + kSplitKeys);
+            const size_t smem = sizeof(float) * ((size_t)D + kSplitKeys + 4 * (size_t)DV);
             dim3 grid(Hq, S, nz);
             count_launch();
 #define LCC_SPLIT(T, VECB)                                                                                                   \
@@ -786,9 +829,9 @@ int attn_chunk_sink(int dt, const float* q, const void* k_pages, const void* v_p
                                                        ld_gate, (T*)out, ld_out, S, Hq, G, D, DV, scale, pos, sink, ld_v, part, counters)
             if (smem > 48 * 1024) return -3;
             if (dt == DT_F32) {
-                if ((D % 4) == 0 && ((uintptr_t)k_pages % 16) == 0) LCC_SPLIT(float, true); else LCC_SPLIT(float, false);
+                if (((D | DV | ld_v) % 4) == 0 && (((uintptr_t)k_pages | (uintptr_t)v_pages) % 16) == 0) LCC_SPLIT(float, true); else LCC_SPLIT(float, false);
             } else {
-                if ((D % 8) == 0 && ((uintptr_t)k_pages % 16) == 0) LCC_SPLIT(bf16, true); else LCC_SPLIT(bf16, false);
+                if (((D | DV | ld_v) % 8) == 0 && (((uintptr_t)k_pages | (uintptr_t)v_pages) % 16) == 0) LCC_SPLIT(bf16, true); else LCC_SPLIT(bf16, false);
             }
 #undef LCC_SPLIT
             return cudaGetLastError() == cudaSuccess ? 0 : -100;
