@@ -21,6 +21,10 @@ struct lcc_seq_model {
     uint8_t* ws = nullptr;
     size_t ws_bytes = 0;
     int cap_tokens = 0, cap_want = 0;
+    // few-row steps run the shared expert beside the router and the routed experts: a second stream, forked and joined by
+    // events (inside a capture these become parallel branches of the graph)
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     bool use_tc = true;  // bf16: large 8-aligned linear layers go to the tcgen05 GEMM, prompt attention to the mma kernel (LIVECC_B200_SEQ_TC=0: never)
 };
 
@@ -70,6 +74,7 @@ inline int ld8(int n) { return (n + 7) / 8 * 8; }
 
 constexpr int kMoeTile = 128;        // row tile of the grouped tensor-core GEMM: expert lists are padded to it on that route
 constexpr int kMoeTcMinRows = 256;   // routed rows (tokens x top) from which the experts run on the tensor cores
+constexpr int kForkMaxRows = 32;     // rows up to which the shared expert runs on the second stream
 
 struct WsLayout {
     size_t x32, xa, proj, proj2, mid, mid2, y32, q32, f1, f2, o1, o2, xf, scan, scan_floats, xsum, moe_f, moe_i, moe_x, moe_h, moe_o, split, split_floats, total;
@@ -268,10 +273,25 @@ lcc_seq_model* lcc_seq_model_create(lcc_ctx* ctx, const lcc_seq_model_desc* desc
     m->d.layers = m->layers.data();
     const char* e = getenv("LIVECC_B200_SEQ_TC");
     m->use_tc = !(e && e[0] == '0');
+    const char* f = getenv("LIVECC_B200_SEQ_FORK");
+    if (!(f && f[0] == '0')) {
+        if (cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&m->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+            cudaGetLastError();
+            m->side = nullptr;      // no second stream: everything stays on the caller's
+        }
+    }
     return m;
 }
 
-void lcc_seq_model_destroy(lcc_seq_model* m) { delete m; }
+void lcc_seq_model_destroy(lcc_seq_model* m) {
+    if (!m) return;
+    if (m->ev_fork) cudaEventDestroy(m->ev_fork);
+    if (m->ev_join) cudaEventDestroy(m->ev_join);
+    if (m->side) cudaStreamDestroy(m->side);
+    delete m;
+}
 
 size_t lcc_seq_workspace_bytes(const lcc_seq_model* m, int max_tokens, int max_want) {
     return m ? make_layout(m, max_tokens, max_want).total : 0;
@@ -527,6 +547,16 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
             // experts on the tensor cores: bf16, enough routed rows, 8-aligned shapes; lists are then padded to whole tiles
             const bool tc = m->use_tc && dt == LCC_DT_BF16 && T * K >= kMoeTcMinRows && (W % 8) == 0 && (l.e_ff % 8) == 0 && W >= 64 && l.e_ff >= 64;
             const int rows_max = T * K + E * (kMoeTile - 1), n_tiles = (rows_max + kMoeTile - 1) / kMoeTile;
+            // the shared expert depends on the normed row only: in few-row steps, where every kernel is latency-bound, it runs on
+            // the second stream beside the router and the routed experts
+            const bool fork = shared && m->side && T <= kForkMaxRows;
+            if (fork && (cudaEventRecord(m->ev_fork, s) != cudaSuccess || cudaStreamWaitEvent(m->side, m->ev_fork, 0) != cudaSuccess))
+                LCC_FAIL(m->ctx, -100, "stream fork failed");
+            if (shared) {
+                cudaStream_t ss = fork ? m->side : s;
+                STEP(linear(m, xa, W, l.e_shared_up, nullptr, mid2, lds, false, T, l.e_shared_ff, W, ss, nullptr, lcc::ACT_RELU2), "shared expert up");
+                STEP(linear(m, mid2, lds, l.e_shared_down, nullptr, o2, W, false, T, W, l.e_shared_ff, ss), "shared expert down");
+            }
             // router logits (and the shared expert's gate logit) accumulate in fp32 from the normed row
             STEP(linear(m, xa, W, l.e_router, nullptr, logit, lde, true, T, E + (shared ? 1 : 0), W, s), "router");
             if (!tc && T * K <= 256 && E <= 512) {
@@ -559,10 +589,8 @@ int lcc_seq_forward(lcc_seq_model* m, const lcc_seq_entry* entries, int n_entrie
                 g.C = eo; g.ldc = ldw8; g.N = W; g.K = l.e_ff; g.act = lcc::ACT_NONE;
                 STEP(lcc::linear_grouped(g, s), "experts down");
             }
-            if (shared) {
-                STEP(linear(m, xa, W, l.e_shared_up, nullptr, mid2, lds, false, T, l.e_shared_ff, W, s, nullptr, lcc::ACT_RELU2), "shared expert up");
-                STEP(linear(m, mid2, lds, l.e_shared_down, nullptr, o2, W, false, T, W, l.e_shared_ff, s), "shared expert down");
-            }
+            if (fork && (cudaEventRecord(m->ev_join, m->side) != cudaSuccess || cudaStreamWaitEvent(s, m->ev_join, 0) != cudaSuccess))
+                LCC_FAIL(m->ctx, -100, "stream join failed");
             if (hc) {   // the weighted sum of the experts' rows is formed by the boundary kernel that folds it into the streams
                 pend_mc = lcc::MoeCombine{eo, ldw8, posn, wsel, K, shared ? o2 : nullptr, W, sgate};
                 pend_is_mc = true;
