@@ -1,6 +1,8 @@
 // Native runtime of the hybrid sequence models: one C call runs a whole step (a prompt portion of any length, or one
 // decode token per sequence) over every layer and produces the logits of the wanted rows. Prefill and decode use the
-// same launch sequence; what differs is the row count and which linear kernel the shape selects.
+// same launch sequence; what differs is the row count and which kernel of an op the shape selects.
+// A layer is a mixer (its output lands in one buffer), a feed-forward (dense or routed) and the block form around them
+// (post-norm residual, or pre-norm sublayers on several residual streams); the three are chosen independently per model.
 // The host (Python) owns every buffer; this file only sequences kernel launches.
 #include <stdlib.h>
 #include <string.h>
