@@ -173,40 +173,44 @@ __global__ void __launch_bounds__(128) attn_split_kernel(const float* __restrict
     for (int k0 = z * kSplitKeys; k0 < nkeys; k0 += nz * kSplitKeys) {
         const int nk = min(kSplitKeys, nkeys - k0);
         __syncthreads();       // sq is staged; the previous tile's weights are consumed
+        // every key's row in the page pool first (one page-table read per thread, all in flight together)
+        for (int j = threadIdx.x; j < nk; j += blockDim.x) {
+            const int pj = k0 + j;
+            row_of[j] = (int)(((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size);
+        }
+        __syncthreads();
         float mx = -INFINITY;
-        // a warp takes four consecutive keys at a time and has all their loads in flight before it sums
-        for (int j0 = warp * 4; j0 < nk; j0 += 16) {
-            const T* kr[4];
+        // a warp takes KG consecutive keys at a time and has all their loads in flight before it sums
+        constexpr int KG = VEC ? 8 : 4;
+        for (int j0 = warp * KG; j0 < nk; j0 += 4 * KG) {
+            const T* kr[KG];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int pj = k0 + min(j0 + j, nk - 1);
-                const size_t ro = ((size_t)page_table[pj / page_size] * G + g) * page_size + pj % page_size;
-                kr[j] = k_pages + ro * D;
-                if (lane == 0 && j0 + j < nk) row_of[j0 + j] = (int)ro;
-            }
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            if (VEC) {
+            for (int j = 0; j < KG; ++j) kr[j] = k_pages + (size_t)row_of[min(j0 + j, nk - 1)] * D;
+            float acc[KG];
+#pragma unroll
+            for (int j = 0; j < KG; ++j) acc[j] = 0.f;
+            if constexpr (VEC) {
                 constexpr int V = RowVec<T>::N;
                 for (int d = lane * V; d < D; d += 32 * V) {
-                    float kv[4][V];
+                    float kv[KG][V];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) RowVec<T>::load(kr[j] + d, kv[j]);
+                    for (int j = 0; j < KG; ++j) RowVec<T>::load(kr[j] + d, kv[j]);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
+                    for (int j = 0; j < KG; ++j)
 #pragma unroll
                         for (int i = 0; i < V; ++i) acc[j] = fmaf(sq[d + i], kv[j][i], acc[j]);
                 }
             } else {
                 for (int d = lane; d < D; d += 32) {
-                    float kv[4];
+                    float kv[KG];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) kv[j] = ldf(kr[j] + d);
+                    for (int j = 0; j < KG; ++j) kv[j] = ldf(kr[j] + d);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) acc[j] = fmaf(sq[d], kv[j], acc[j]);
+                    for (int j = 0; j < KG; ++j) acc[j] = fmaf(sq[d], kv[j], acc[j]);
                 }
             }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < KG; ++j) {
                 const float v = warp_sum(acc[j]);
                 if (j0 + j < nk) {
                     if (lane == 0) sc[j0 + j] = v;
