@@ -208,15 +208,6 @@ __global__ void __launch_bounds__(256) gather_rmsnorm_kernel(const float* __rest
     for (int c = threadIdx.x; c < W; c += blockDim.x) stf(out + (size_t)i * W + c, x[c] * rn * w[c]);
 }
 
-template <typename T>
-__global__ void relu_squared_kernel(const T* __restrict__ in, int ld_in, T* __restrict__ out, int ld_out, int S, int n) {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (int64_t)S * n) return;
-    const int r = (int)(i / n), c = (int)(i % n);
-    const float z = fmaxf(ldf(in + (size_t)r * ld_in + c), 0.f);
-    stf(out + (size_t)r * ld_out + c, z * z);
-}
-
 __global__ void softcap_kernel(float* __restrict__ x, int64_t n, float cap, float inv_cap) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] = cap * tanhf(x[i] * inv_cap);
@@ -296,17 +287,6 @@ int glu_gelu_tanh(int dt, const void* gu, int ld, void* out, int ld_out, int S, 
         glu_gelu_tanh_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const float*)gu, ld, (float*)out, ld_out, S, F);
     else
         glu_gelu_tanh_kernel<bf16><<<(unsigned)((n + 255) / 256), 256, 0, s>>>((const bf16*)gu, ld, (bf16*)out, ld_out, S, F);
-    return done();
-}
-
-int relu_squared(int dt, const void* in, int ld_in, void* out, int ld_out, int S, int n, cudaStream_t s) {
-    if (!in || !out || S < 1 || n < 1) return -2;
-    const int64_t tot = (int64_t)S * n;
-    count_launch();
-    if (dt == DT_F32)
-        relu_squared_kernel<float><<<(unsigned)((tot + 255) / 256), 256, 0, s>>>((const float*)in, ld_in, (float*)out, ld_out, S, n);
-    else
-        relu_squared_kernel<bf16><<<(unsigned)((tot + 255) / 256), 256, 0, s>>>((const bf16*)in, ld_in, (bf16*)out, ld_out, S, n);
     return done();
 }
 

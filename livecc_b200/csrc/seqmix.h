@@ -50,8 +50,6 @@ struct GroupedLinear {
 };
 enum { ACT_NONE = 0, ACT_RELU2 = 1 };
 int linear_grouped(const GroupedLinear& g, cudaStream_t s);
-// out[r, c] = relu(in[r, c])^2  (storage dt)
-int relu_squared(int dt, const void* in, int ld_in, void* out, int ld_out, int S, int n, cudaStream_t s);
 
 // ---- recurrent.cu -------------------------------------------------------------------------------------------------------
 // Causal per-channel convolution over `taps` inputs followed by silu. in/out: [S, C] slices (storage dt, leading

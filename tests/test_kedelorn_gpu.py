@@ -285,6 +285,26 @@ def test_experts_on_the_tensor_cores(monkeypatch):
     assert rel(run(build(d, tensors, "float32"), toks, []), want) < F32_TOL
 
 
+def test_routed_feed_forward_in_post_norm_blocks(monkeypatch):
+    """The routed feed-forward is a mechanism of the family, not of one design: state-space and parallel layers in post-norm
+    blocks with routed experts, where the weighted sum of the expert rows is a kernel of its own before the post-norm
+    residual. The post-norm oracle gets this file's routed feed-forward in place of its dense one."""
+    import seq_cases
+    import seq_oracle
+
+    mlp = K.moe(experts=6, top=2, ff=16, scale=1.5, shared=24)
+    layers = [dict(seq_cases.ssd(), mlp=mlp), dict(seq_cases.par(), mlp=mlp)]
+    d = seq_cases.config(layers, width=40)
+    tensors = synthetic_seq_tensors(SeqModelConfig.from_json(d), seed=26)
+    monkeypatch.setattr(seq_oracle, "feed_forward",
+                        lambda h, w, pre: O.routed_ff(h, {k[len(pre):]: v for k, v in w.items() if k.startswith(pre)}, mlp))
+    toks = K.tokens(120, d["vocab"], seed=55)
+    want = seq_oracle.forward(d, tensors, toks)[0]
+    m = build(d, tensors)
+    assert rel(run(m, toks, []), want) < F32_TOL
+    assert rel(run(m, toks, [50, 52] + list(range(100, 120))), want) < F32_TOL
+
+
 # ---- batches, pages and slots that are used again -----------------------------------------------------------------------------
 def test_a_batch_of_unequal_requests_equals_each_alone():
     m, d, _ = model_of("mixed")
