@@ -384,6 +384,19 @@ def test_greedy_generation_through_the_engine_entry_point():
     assert len(got) == 8 and all(0 <= t < d["vocab"] for t in got)
 
 
+def test_generation_grows_across_key_tiles():
+    """A replayed decode step was captured when the window held 100 keys; 200 tokens later it holds 300, which is three key
+    tiles for the one split the captured grid has. Every step's logits against the oracle over the generated sequence."""
+    m, d, tensors = model_of("latent_only")
+    prompt = K.tokens(100, d["vocab"], seed=10)
+    out = m.generate(torch.tensor([prompt]), max_new_tokens=200, eos_token_id=-1, output_logits=True)
+    seq = out.sequences[0].tolist()
+    assert len(seq) == 300 and seq[:100] == prompt
+    want = O.forward(d, tensors, seq)[0][99:299]
+    assert rel(torch.stack(out.logits), want) < 2 * F32_TOL
+    out.past_key_values.release()
+
+
 def test_trace_replay_command_line(tmp_path):
     d = K.CASES["mixed"]
     tensors = synthetic_seq_tensors(SeqModelConfig.from_json(d), seed=21)
