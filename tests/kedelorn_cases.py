@@ -58,3 +58,40 @@ CASES = {
 def tokens(n, vocab, seed=0):
     g = torch.Generator().manual_seed(2000 + seed)
     return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def random_config(seed):
+    """A random stack: 2 to 6 layers in any order, 1 to 8 streams, head counts, key / value / latent / rotary sizes that are
+    and are not multiples of 8, caches read by later layers, routers from 1 to 40 experts, layers without feed-forward."""
+    import random
+
+    rng = random.Random(seed)
+
+    def rmoe():
+        if rng.random() < 0.2:
+            return None
+        E = rng.choice([1, 2, 3, 6, 8, 12, 17, 40])
+        return moe(experts=E, top=rng.randint(1, min(E, 5)), ff=rng.choice([8, 12, 16, 40, 64]), scale=rng.choice([0.5, 1.0, 2.5]),
+                   shared=rng.choice([0, 8, 20, 64]))
+
+    layers, owners = [], []
+    for i in range(rng.randint(2, 6)):
+        if rng.random() < 0.5:
+            H, dim = rng.choice([1, 2, 3, 5]), rng.choice([6, 8, 16, 20, 32, 72])
+            layers.append(ret(heads=H, dim=dim, vdim=rng.choice([4, 8, 12, 40, 72]), decay=[1.0 - 2.0 ** -rng.uniform(1, 10) for _ in range(H)],
+                              rot_dims=rng.choice([0, 2, dim // 2 // 2 * 2, dim]), base=rng.choice([100.0, 1e4, 1e6]), mlp=rmoe()))
+        elif owners and rng.random() < 0.4:
+            j = rng.choice(owners)              # reads layer j's cache: same latent and rotary geometry, its own heads
+            g = layers[j]["mixer"]
+            L = lat(heads=rng.choice([1, 2, 4, 7]), dim=rng.choice([4, 8, 12, 32]), rot_dim=g["rot_dim"], vdim=rng.choice([4, 8, 20, 32]),
+                    kv_rank=g["kv_rank"], scale=rng.uniform(0.05, 0.5), kv_from=j, mlp=rmoe())
+            L["mixer"]["rot"] = dict(g["rot"])
+            layers.append(L)
+        else:
+            owners.append(i)
+            layers.append(lat(heads=rng.choice([1, 2, 3, 6]), dim=rng.choice([4, 8, 12, 32, 64]), rot_dim=rng.choice([2, 6, 8, 16, 32]),
+                              vdim=rng.choice([4, 8, 20, 32]), kv_rank=rng.choice([8, 12, 20, 64, 136]), scale=rng.uniform(0.05, 0.5),
+                              base=rng.choice([300.0, 1e4, 5e5]),
+                              scaling=rng.choice([None, (2.0, 64, 16.0, 1.0), (4.0, 32, 8.0, 2.0), (8.0, 1024, 32.0, 0.5)]), mlp=rmoe()))
+    return config(layers, width=rng.choice([16, 24, 40, 64, 100, 136]), vocab=rng.choice([50, 96, 200]), streams=rng.choice([1, 2, 3, 4, 5, 8]),
+                  eps=rng.choice([1e-6, 1e-5]))

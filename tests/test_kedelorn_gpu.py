@@ -117,6 +117,33 @@ def test_the_sink_and_the_router_correction_show_in_these_weights():
     assert rel(got, oracle("mixed", toks, correction=False)[0]) > 100 * F32_TOL
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations_in_three_schedules(seed):
+    """Random stacks (tests/kedelorn_cases.py::random_config): the whole prompt, most of it then token by token, and portions of
+    changing size down to two tokens, all against the oracle in fp32. bf16 storage runs every stack (finite logits) and is
+    held to rounding where the stack is shallow: through six narrow layers of unit-norm heads and routers, rounding noise
+    grows past any fixed bound."""
+    import random
+
+    d = K.random_config(seed)
+    tensors = synthetic_seq_tensors(SeqModelConfig.from_json(d), seed=30 + seed)
+    rng = random.Random(seed)
+    T = rng.choice([70, 150, 260])
+    toks = K.tokens(T, d["vocab"], seed=60 + seed)
+    want = O.forward(d, tensors, toks)[0]
+    portions, p = [], 0
+    while p < T - 20:
+        p += rng.choice([2, 3, 5, 16, 37, 64])
+        portions.append(min(p, T - 20))
+    m = build(d, tensors)
+    for cuts in ([], [T - 20] + list(range(T - 19, T)), portions + list(range(T - 19, T))):
+        assert rel(run(m, toks, cuts), want) < F32_TOL
+    got = run(build(d, tensors, "bfloat16"), toks, portions)
+    assert bool(torch.isfinite(got).all())
+    if len(d["layers"]) <= 3:
+        assert bf16_ok(got, want)
+
+
 # ---- prefill against decoding, portions, first tokens ---------------------------------------------------------------------
 @pytest.mark.parametrize("name", ALL)
 def test_token_by_token_decoding_equals_the_whole_prompt(name):
